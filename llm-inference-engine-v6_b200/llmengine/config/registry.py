@@ -17,11 +17,14 @@ class Architecture:
     """name: value of config.json `architectures[0]`.
     parse_config(config_json, generation_config_json|None) -> typed configuration.
     describe(config) -> parts.spec.ModelSpec (layers, their order, the tensors they need).
-    config_to_json(config) -> dict written as config.json by the random-weights mode."""
+    config_to_json(config) -> dict written as config.json by the random-weights mode.
+    sizes_from_tensors(config_json, shape_of) -> config_json (optional): for a design some of whose sizes are given by tensor
+    shapes alone; called when a model folder is opened, with shape_of(name) -> the checkpoint's shape of a tensor or None."""
     name: str
     parse_config: Callable[[Dict[str, Any], Optional[Dict[str, Any]]], Any]
     describe: Callable[[Any], Any]
     config_to_json: Callable[[Any], Dict[str, Any]]
+    sizes_from_tensors: Optional[Callable[[Dict[str, Any], Callable[[str], Any]], Dict[str, Any]]] = None
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}
@@ -61,4 +64,8 @@ def config_from_dir(model_dir: str):
     """-> (Architecture, typed configuration) for the model folder."""
     j = read_config_json(model_dir)
     arch = get_architecture(architecture_name_of(j))
+    if arch.sizes_from_tensors is not None:
+        from ..weights.loader import Checkpoint  # only the files' headers are read here
+        ckpt = Checkpoint(model_dir)
+        j = arch.sizes_from_tensors(j, lambda name: tuple(ckpt.shape(name)) if name in ckpt else None)
     return arch, arch.parse_config(j, read_generation_config_json(model_dir))

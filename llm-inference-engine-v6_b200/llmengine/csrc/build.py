@@ -38,7 +38,7 @@ CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-fvisibility=hidden", "-Wall", "-Wex
 # name -> CUDA sources. "core" is what every model and precision needs; "tensorcore" holds the
 # tcgen05/TMA kernels that only the bfloat16 path uses.
 KERNEL_LIBRARIES: Dict[str, List[str]] = {
-    "core": ["status.cu", "elementwise.cu", "gemm_simt.cu", "rope_kv.cu", "attention_simt.cu", "latent.cu", "routed.cu", "gated_attention.cu", "selective_scan.cu", "sampling.cu"],
+    "core": ["status.cu", "elementwise.cu", "gemm_simt.cu", "rope_kv.cu", "attention_simt.cu", "latent.cu", "routed.cu", "gated_attention.cu", "selective_scan.cu", "linear_state.cu", "sampling.cu"],
     "tensorcore": ["status.cu", "gemm_tc.cu", "gemm_decode.cu", "attention_mma.cu", "attention_tc.cu", "attention_decode.cu", "latent_mma.cu", "routed_mma.cu"],
 }
 HOST_SOURCES = ["cache_manager.cpp", "scheduler.cpp", "bindings.cpp"]

@@ -33,7 +33,7 @@ struct AttnParams {
   const bf16* kcache; const bf16* vcache;
   const int* seq_start; const int* seq_ntok; const int* seq_qoff; const int* block_table;
   int max_blocks, nq, nkv, page_size, window;
-  int chunk; const float* sink; const float* gate; int g_parts; long long g_pstride; int g_width, g_off;
+  int chunk; const float* sink; const float* gate; int g_parts; long long g_pstride; int g_width, g_off, g_head;  // g_head 1: one gate a head (column g_off + head)
   float scale;
   bf16* out; long long ld_out;
   // split mode (decode): partial outputs [split][token][head][HD] and (max, sum) [split][token][head][2]
@@ -260,18 +260,19 @@ __global__ void __launch_bounds__(THREADS) paged_attention_mma_kernel(const Attn
     const float inv = half ? inv_b : inv_a;
     if (!SPLIT) {
       bf16* dst = p.out + (size_t)(tok_base + tq) * p.ld_out + (size_t)(kvh * g + hg) * HDV + 2 * (lane % 4);
-      const size_t gcol = (size_t)(tok_base + tq) * p.g_width + p.g_off + (size_t)(kvh * g + hg) * HDV + 2 * (lane % 4);
+      const size_t gcol = (size_t)(tok_base + tq) * p.g_width + p.g_off + (p.g_head ? (size_t)(kvh * g + hg) : (size_t)(kvh * g + hg) * HDV + 2 * (lane % 4));
+      const int gd = p.g_head ? 0 : 8, g1 = p.g_head ? 0 : 1;  // steps of the gate's column along the result
 #pragma unroll
       for (int d = 0; d < DTILES; ++d) {
         float v0 = o_acc[d][2 * half] * inv, v1 = o_acc[d][2 * half + 1] * inv;
         if (p.gate != nullptr) {  // times sigmoid of the gate's sums, added in index order
-          float g0 = p.gate[gcol + d * 8], g1 = p.gate[gcol + d * 8 + 1];
+          float ga = p.gate[gcol + d * gd], gb = p.gate[gcol + d * gd + g1];
           for (int k = 1; k < p.g_parts; ++k) {
-            g0 += p.gate[(size_t)k * p.g_pstride + gcol + d * 8];
-            g1 += p.gate[(size_t)k * p.g_pstride + gcol + d * 8 + 1];
+            ga += p.gate[(size_t)k * p.g_pstride + gcol + d * gd];
+            gb += p.gate[(size_t)k * p.g_pstride + gcol + d * gd + g1];
           }
-          v0 = v0 / (1.0f + expf(-g0));
-          v1 = v1 / (1.0f + expf(-g1));
+          v0 = v0 / (1.0f + expf(-ga));
+          v1 = v1 / (1.0f + expf(-gb));
         }
         *reinterpret_cast<uint32_t*>(dst + d * 8) = pack_bf16(v0, v1);
       }
@@ -298,7 +299,7 @@ template <int HD>
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int n_splits,
                                          long long part_stride_tokens, int nq, bf16* __restrict__ out, long long ld_out,
                                          int n_tokens, const float* __restrict__ sink, const float* __restrict__ gate, int g_parts,
-                                         long long g_pstride, int g_width, int g_off) {
+                                         long long g_pstride, int g_width, int g_off, int g_head) {
   dep_launch();
   dep_wait();
   const int item = blockIdx.x * (blockDim.x / 32) + (threadIdx.x >> 5);
@@ -351,7 +352,7 @@ __global__ void attention_combine_kernel(const float* __restrict__ part_o, const
     if (d < HD) {
       float v = acc[i] * inv;
       if (gate) {
-        const size_t col = (size_t)tok * g_width + g_off + (size_t)head * HD + d;
+        const size_t col = (size_t)tok * g_width + g_off + (g_head ? (size_t)head : (size_t)head * HD + d);
         float g = gate[col];
         for (int k = 1; k < g_parts; ++k) g += gate[(size_t)k * g_pstride + col];
         v = v / (1.0f + expf(-g));
@@ -391,7 +392,7 @@ int launch(const AttnParams& p, int n_seqs, int max_new_tokens, int n_tokens, bo
     const int items = n_tokens * p.nq;
     launch_kernel(attention_combine_kernel<HD>, (items + 3) / 4, 128, 0, stream, (const float*)p.part_o, (const float*)p.part_ml,
                   p.n_splits, p.part_stride_tokens, p.nq, p.out, p.ld_out, n_tokens, p.sink, p.gate, p.g_parts, p.g_pstride, p.g_width,
-                  p.g_off);
+                  p.g_off, p.g_head);
   } else {
     if (!set_attr(paged_attention_mma_kernel<HD, HD, false>, smem)) return 1;
     launch_kernel(paged_attention_mma_kernel<HD, HD, false>, grid, THREADS, smem, stream, p);
@@ -436,7 +437,7 @@ extern "C" int llm_paged_attention_mma(const void* q, long long ld_q, const void
   p.seq_start = seq_start; p.seq_ntok = seq_ntok; p.seq_qoff = seq_qoff; p.block_table = block_table;
   p.max_blocks = max_blocks; p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.window = window; p.scale = scale;
   p.out = (bf16*)out; p.ld_out = ld_out;
-  p.chunk = 0; p.sink = nullptr; p.gate = nullptr; p.g_parts = 0; p.g_pstride = 0; p.g_width = 0; p.g_off = 0;
+  p.chunk = 0; p.sink = nullptr; p.gate = nullptr; p.g_parts = 0; p.g_pstride = 0; p.g_width = 0; p.g_off = 0; p.g_head = 0;
   p.n_splits = n_splits; p.split_keys = split_keys; p.part_stride_tokens = n_tokens;
   p.part_o = scratch; p.part_ml = scratch ? scratch + (size_t)n_splits * n_tokens * nq * hd : nullptr;
   const bool split = n_splits > 1;
@@ -466,7 +467,7 @@ extern "C" int llm_gated_attention_mma(const void* q, long long ld_q, const void
                                        const int* seq_ntok, const int* seq_qoff, const int* block_table, int max_blocks, void* out,
                                        long long ld_out, int n_seqs, int max_new_tokens, int nq, int nkv, int dk, int dv, int page_size,
                                        float scale, int window, int chunk, const float* sink, const float* gate, int g_parts,
-                                       long long g_pstride, int g_width, int g_off, int n_tokens, int n_splits, int split_keys,
+                                       long long g_pstride, int g_width, int g_off, int g_head, int n_tokens, int n_splits, int split_keys,
                                        float* scratch, cudaStream_t stream) {
   if (n_seqs == 0 || max_new_tokens == 0) return LLM_OK;
   LLM_REQUIRE(n_splits >= 1 && (n_splits == 1 || (dk == dv && max_new_tokens == 1 && split_keys > 0 && split_keys % N_TILE == 0 && scratch != nullptr)),
@@ -476,14 +477,14 @@ extern "C" int llm_gated_attention_mma(const void* q, long long ld_q, const void
   LLM_REQUIRE(page_size > 0 && max_blocks > 0 && window >= 0 && chunk >= 0 && max_new_tokens > 0, "gated_attention_mma: bad sizes");
   LLM_REQUIRE((reinterpret_cast<uintptr_t>(q) & 15u) == 0 && (reinterpret_cast<uintptr_t>(kcache) & 15u) == 0 &&
               (reinterpret_cast<uintptr_t>(vcache) & 15u) == 0, "gated_attention_mma: q and the caches must be 16-byte aligned");
-  LLM_REQUIRE(gate == nullptr || (g_parts >= 1 && g_off >= 0 && (long long)g_off + (long long)nq * dv <= g_width), "gated_attention_mma: gate columns outside the product");
+  LLM_REQUIRE(gate == nullptr || (g_parts >= 1 && g_off >= 0 && (long long)g_off + (long long)nq * (g_head ? 1 : dv) <= g_width), "gated_attention_mma: gate columns outside the product");
   LLM_REQUIRE((long long)n_seqs <= 65535 && nkv <= 65535, "gated_attention_mma: batch too large for the grid");
   AttnParams p;
   p.q = (const bf16*)q; p.ld_q = ld_q; p.kcache = (const bf16*)kcache; p.vcache = (const bf16*)vcache;
   p.seq_start = seq_start; p.seq_ntok = seq_ntok; p.seq_qoff = seq_qoff; p.block_table = block_table;
   p.max_blocks = max_blocks; p.nq = nq; p.nkv = nkv; p.page_size = page_size; p.window = window; p.scale = scale;
   p.out = (bf16*)out; p.ld_out = ld_out;
-  p.chunk = chunk; p.sink = sink; p.gate = gate; p.g_parts = g_parts; p.g_pstride = g_pstride; p.g_width = g_width; p.g_off = g_off;
+  p.chunk = chunk; p.sink = sink; p.gate = gate; p.g_parts = g_parts; p.g_pstride = g_pstride; p.g_width = g_width; p.g_off = g_off; p.g_head = g_head;
   p.n_splits = n_splits; p.split_keys = split_keys; p.part_stride_tokens = n_tokens;
   p.part_o = scratch; p.part_ml = scratch ? scratch + (size_t)n_splits * n_tokens * nq * dv : nullptr;
   int rc = 1;

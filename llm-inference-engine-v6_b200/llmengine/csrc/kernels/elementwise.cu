@@ -255,13 +255,23 @@ __device__ __forceinline__ void gate_up_columns(int c, int ff, int block, size_t
 }
 
 // act 0: silu, g / (1 + exp(-g)); act 1: the tanh form of gelu, 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3)))
+// act 2: both sides limited, a sigmoid of slope p1 on the gate, the up side raised by one:
+//        g <- min(g, p0), u <- clamp(u, -p0, p0), result g * sigmoid(p1 * g) * (u + 1)
 __device__ __forceinline__ float gate_activation(float g, int act) {
   if (act == 1) return 0.5f * g * (1.0f + tanhf(0.79788456080286535588f * (g + 0.044715f * g * g * g)));
   return g / (1.0f + expf(-g));
 }
+__device__ __forceinline__ float gated_value(float g, float u, int act, float p0, float p1) {
+  if (act == 2) {
+    g = fminf(g, p0);
+    u = fminf(fmaxf(u, -p0), p0);
+    return g / (1.0f + expf(-p1 * g)) * (u + 1.0f);
+  }
+  return gate_activation(g, act) * u;
+}
 
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, int ff, size_t total, int block, int act) {
+__global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, int ff, size_t total, int block, int act, float p0, float p1) {
   dep_launch();
   dep_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -272,21 +282,20 @@ __global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, i
   gate_up_columns(c, ff, block, &gc, &uc);
   const float g = to_f32(in[r * 2 * ff + gc]);
   const float u = to_f32(in[r * 2 * ff + uc]);
-  float s = gate_activation(g, act);
-  out[i] = from_f32<T>(s * u);
+  out[i] = from_f32<T>(gated_value(g, u, act, p0, p1));
 }
 
-extern "C" int llm_silu_mul(const void* in, void* out, int dtype, int n_rows, int ff, int block, int act, cudaStream_t stream) {
+extern "C" int llm_silu_mul(const void* in, void* out, int dtype, int n_rows, int ff, int block, int act, float p0, float p1, cudaStream_t stream) {
   if (n_rows == 0) return LLM_OK;
   LLM_REQUIRE(n_rows > 0 && ff > 0, "silu_mul: bad sizes rows=%d ff=%d", n_rows, ff);
   LLM_REQUIRE(block >= 0 && (block == 0 || ff % block == 0), "silu_mul: column block %d does not divide %d", block, ff);
-  LLM_REQUIRE(act == 0 || act == 1, "silu_mul: unknown activation %d", act);
+  LLM_REQUIRE(act >= 0 && act <= 2, "silu_mul: unknown activation %d", act);
   const size_t total = (size_t)n_rows * ff;
   const int blocks = ceil_div((long long)total, 256);
   if (dtype == LLM_F32)
-    launch_kernel(silu_mul_kernel<float>, blocks, 256, 0, stream, (const float*)in, (float*)out, ff, total, block, act);
+    launch_kernel(silu_mul_kernel<float>, blocks, 256, 0, stream, (const float*)in, (float*)out, ff, total, block, act, p0, p1);
   else if (dtype == LLM_BF16)
-    launch_kernel(silu_mul_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)in, (bf16*)out, ff, total, block, act);
+    launch_kernel(silu_mul_kernel<bf16>, blocks, 256, 0, stream, (const bf16*)in, (bf16*)out, ff, total, block, act, p0, p1);
   else
     LLM_REQUIRE(false, "silu_mul: unknown dtype %d", dtype);
   LLM_CHECK_LAUNCH("silu_mul");
@@ -326,7 +335,7 @@ extern "C" int llm_reduce_partials(const float* partials, int n_partials, long l
 // partials: [parts, rows, 2*ff] float32 (gate | up); out [rows, ff] = silu(sum gate) * (sum up).
 template <typename T>
 __global__ void silu_mul_partials_kernel(const float* __restrict__ partials, int n_partials, size_t stride,
-                                         T* __restrict__ out, int ff, size_t total, int block, const RowScale rs, int act) {
+                                         T* __restrict__ out, int ff, size_t total, int block, const RowScale rs, int act, float p0, float p1) {
   dep_launch();
   dep_wait();
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -354,23 +363,23 @@ __global__ void silu_mul_partials_kernel(const float* __restrict__ partials, int
   const float sc = row_scale(rs, r);  // the norm before the product, when its 1/rms is still owed
   g *= sc;
   u *= sc;
-  const float s = gate_activation(g, act);
-  out[i] = from_f32<T>(s * u);
+  out[i] = from_f32<T>(gated_value(g, u, act, p0, p1));
 }
 
 extern "C" int llm_silu_mul_partials(const float* partials, int n_partials, long long stride, void* out, int out_dtype,
                                      int n_rows, int ff, int block, const float* sumsq, int n_sumsq, float inv_dim, float eps,
-                                     int act, cudaStream_t stream) {
+                                     int act, float p0, float p1, cudaStream_t stream) {
   if (n_rows == 0) return LLM_OK;
+  LLM_REQUIRE(act >= 0 && act <= 2, "silu_mul_partials: unknown activation %d", act);
   const RowScale rs{sumsq, n_sumsq, inv_dim, eps};
   LLM_REQUIRE(n_rows > 0 && ff > 0 && n_partials >= 1, "silu_mul_partials: bad sizes");
   LLM_REQUIRE(block >= 0 && (block == 0 || ff % block == 0), "silu_mul_partials: column block %d does not divide %d", block, ff);
   const size_t total = (size_t)n_rows * ff;
   const int blocks = ceil_div((long long)total, 256);
   if (out_dtype == LLM_F32)
-    launch_kernel(silu_mul_partials_kernel<float>, blocks, 256, 0, stream, partials, n_partials, (size_t)stride, (float*)out, ff, total, block, rs, act);
+    launch_kernel(silu_mul_partials_kernel<float>, blocks, 256, 0, stream, partials, n_partials, (size_t)stride, (float*)out, ff, total, block, rs, act, p0, p1);
   else if (out_dtype == LLM_BF16)
-    launch_kernel(silu_mul_partials_kernel<bf16>, blocks, 256, 0, stream, partials, n_partials, (size_t)stride, (bf16*)out, ff, total, block, rs, act);
+    launch_kernel(silu_mul_partials_kernel<bf16>, blocks, 256, 0, stream, partials, n_partials, (size_t)stride, (bf16*)out, ff, total, block, rs, act, p0, p1);
   else
     LLM_REQUIRE(false, "silu_mul_partials: unknown dtype %d", out_dtype);
   LLM_CHECK_LAUNCH("silu_mul_partials");
@@ -629,5 +638,50 @@ extern "C" int llm_norm_add(float* h, const float* a, int na, long long sa, cons
   else { if (keep) LLM_NA(bf16, true); else LLM_NA(bf16, false); }
 #undef LLM_NA
   LLM_CHECK_LAUNCH("norm_add");
+  return LLM_OK;
+}
+
+// ------------------------------------------------------------------------------------ two branches into one
+// out[r] = ca * fa(a[r]) + cb * fb(b[r]) for two sets of float32 sums (parts added in index order): f is the identity, or, with a
+// weight, the row divided by its root mean square (eps inside the root) times that weight. One block a row, float32.
+namespace {
+__global__ void __launch_bounds__(256)
+    pair_combine_kernel(const float* __restrict__ a, int na, size_t sa, const float* __restrict__ b, int nb, size_t sb,
+                        const float* __restrict__ wa, const float* __restrict__ wb, float ca, float cb, float eps, float* __restrict__ out, int dim) {
+  __shared__ float red[33];
+  dep_launch();
+  dep_wait();
+  const size_t base = (size_t)blockIdx.x * dim;
+  auto sum_of = [&](const float* p, int n, size_t stride, int i) {
+    float y = p[base + i];
+    for (int k = 1; k < n; ++k) y += p[(size_t)k * stride + base + i];
+    return y;
+  };
+  float inv_a = 1.0f, inv_b = 1.0f;
+  if (wa) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) { const float y = sum_of(a, na, sa, i); ss += y * y; }
+    inv_a = 1.0f / sqrtf(block_sum(ss, red) / (float)dim + eps);
+  }
+  if (wb) {
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) { const float y = sum_of(b, nb, sb, i); ss += y * y; }
+    inv_b = 1.0f / sqrtf(block_sum(ss, red) / (float)dim + eps);
+  }
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    float ya = sum_of(a, na, sa, i), yb = sum_of(b, nb, sb, i);
+    if (wa) ya = ya * inv_a * wa[i];
+    if (wb) yb = yb * inv_b * wb[i];
+    out[base + i] = ca * ya + cb * yb;
+  }
+}
+}  // namespace
+
+extern "C" int llm_pair_combine(const float* a, int na, long long sa, const float* b, int nb, long long sb, const float* wa, const float* wb,
+                                float ca, float cb, float eps, float* out, int n_rows, int dim, cudaStream_t stream) {
+  if (n_rows == 0) return LLM_OK;
+  LLM_REQUIRE(n_rows > 0 && dim > 0 && a && b && na >= 1 && nb >= 1 && out, "pair_combine: bad arguments");
+  launch_kernel(pair_combine_kernel, n_rows, 256, 0, stream, a, na, (size_t)sa, b, nb, (size_t)sb, wa, wb, ca, cb, eps, out, dim);
+  LLM_CHECK_LAUNCH("pair_combine");
   return LLM_OK;
 }

@@ -9,7 +9,7 @@
 //   attention  one warp a (token, query head): keys lo..pos of the request through its block table, lo = the later of the
 //              window's and the chunk's start (a chunk is [c * size, (c + 1) * size) in absolute positions); softmax in float32
 //              whose denominator also holds exp(sink[head]) (optional: a learned term of the denominator alone); the result times
-//              sigmoid(gate) (optional, float32 partial sums of the same product) before it is rounded.
+//              sigmoid(gate) (optional, float32 partial sums of the same product; a gate a number or one a head) before it is rounded.
 //
 // Keys are walked in chunks of 32 aligned to absolute positions, so a token's result does not depend on how its request was
 // cut into steps, on the rest of the batch or on page numbers.
@@ -100,7 +100,7 @@ __global__ void __launch_bounds__(WARPS * 32)
                                 const int* __restrict__ positions, const int* __restrict__ token_seq, const int* __restrict__ block_table,
                                 int max_blocks, T* __restrict__ out, long long ld_out, int n_tokens, int nq, int nkv, int dk, int dv,
                                 int page_size, float scale, int window, int chunk, const float* __restrict__ sink,
-                                const float* __restrict__ gate, int g_parts, size_t g_pstride, int g_width, int g_off) {
+                                const float* __restrict__ gate, int g_parts, size_t g_pstride, int g_width, int g_off, int g_head) {
   __shared__ float q_s[WARPS][MAX_HD];
   dep_launch();
   dep_wait();
@@ -173,7 +173,7 @@ __global__ void __launch_bounds__(WARPS * 32)
     if (d < dv) {
       float v = acc[i] * inv;
       if (gate) {
-        const float g = parts_sum(gate, g_parts, g_pstride, (size_t)tok * g_width + g_off + (size_t)head * dv + d);
+        const float g = parts_sum(gate, g_parts, g_pstride, (size_t)tok * g_width + g_off + (g_head ? (size_t)head : (size_t)head * dv + d));
         v = v / (1.0f + expf(-g));
       }
       o[d] = from_f32<T>(v);
@@ -215,18 +215,19 @@ extern "C" int llm_gated_attention_simt(const void* q, long long ld_q, const voi
                                         const int* positions, const int* token_seq, const int* block_table, int max_blocks, void* out,
                                         long long ld_out, int n_tokens, int nq, int nkv, int dk, int dv, int page_size, float scale,
                                         int window, int chunk, const float* sink, const float* gate, int g_parts, long long g_pstride,
-                                        int g_width, int g_off, cudaStream_t stream) {
+                                        int g_width, int g_off, int g_head, cudaStream_t stream) {
+  // g_head 0: a gate a number of the result (columns g_off + head * dv + d); 1: one gate a head (column g_off + head)
   if (n_tokens == 0) return LLM_OK;
   LLM_REQUIRE(n_tokens > 0 && nq > 0 && nkv > 0 && nq % nkv == 0, "attention: bad head counts nq=%d nkv=%d", nq, nkv);
   LLM_REQUIRE(dk > 0 && dk <= MAX_HD && dv > 0 && dv <= MAX_HD, "attention: head sizes %d / %d not in 1..%d", dk, dv, MAX_HD);
   LLM_REQUIRE(page_size > 0 && max_blocks > 0 && window >= 0 && chunk >= 0, "attention: bad page_size/max_blocks/window/chunk");
-  LLM_REQUIRE(gate == nullptr || (g_parts >= 1 && g_off >= 0 && (long long)g_off + (long long)nq * dv <= g_width), "attention: gate columns outside the product");
+  LLM_REQUIRE(gate == nullptr || (g_parts >= 1 && g_off >= 0 && (long long)g_off + (long long)nq * (g_head ? 1 : dv) <= g_width), "attention: gate columns outside the product");
   const long long items = (long long)n_tokens * nq;
   const int grid = ceil_div(items, WARPS);
 #define LLM_GA(T, R)                                                                                                                 \
   launch_kernel(gated_attention_simt_kernel<T, R>, grid, WARPS * 32, 0, stream, (const T*)q, ld_q, (const T*)kcache, (const T*)vcache, \
                 positions, token_seq, block_table, max_blocks, (T*)out, ld_out, n_tokens, nq, nkv, dk, dv, page_size, scale, window,   \
-                chunk, sink, gate, g_parts, (size_t)g_pstride, g_width, g_off)
+                chunk, sink, gate, g_parts, (size_t)g_pstride, g_width, g_off, g_head)
 #define LLM_GA_R(T)            \
   if (dv <= 32) LLM_GA(T, 1);  \
   else if (dv <= 64) LLM_GA(T, 2); \

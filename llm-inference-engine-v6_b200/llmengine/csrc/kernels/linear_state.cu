@@ -1,0 +1,331 @@
+// Mixers whose memory is a matrix per head ("linear state"): S [dk, dv] per request and head, float32, kept in the request's state
+// slot, updated token after token by a rank-one write k v^T and read by a query. Three update rules share one kernel:
+//
+//   MODE 0  decay a key channel, write, read:   S <- diag(a_t) S + k_t v_t^T;              o_t = S^T q_t
+//   MODE 1  read with a bonus, decay, write:    o_t = (S + diag(u) k_t v_t^T)^T q_t;       S <- diag(a_t) S + k_t v_t^T
+//   MODE 2  delta rule with a decay a head:     S <- g_t S;  w = beta_t (v_t - S^T k_t);   S <- S + k_t w^T;   o_t = S^T q_t
+//           (q and k made unit vectors per head first: x / sqrt(sum x^2 + unit_eps))
+//
+// Every column S[:, j] evolves by itself, so a block takes a (request, head, tile of columns) and walks the request's tokens of the
+// step in order; a column's dk numbers are spread over R lanes of a warp (KPT = 16 numbers a lane), the two dot products of a
+// token are sums over a lane's numbers and then over the R lanes (xor shuffles, a fixed order). The tokens' q, k, decays and v
+// come through shared memory in tiles of a few tokens (a warp a token: the sums of the products' parts, the unit norms and the
+// query's scale are applied there), so the walk itself only syncs once a tile. Results never depend on how a request was cut into
+// steps, on the batch or on the slot: the same additions happen in the same order.
+//
+// In the slot a head's matrix is stored as the threads hold it: number (m, column j, lane r) at ((m * dv + j) * R + r), which is
+// S[r + R * m, j]; loads and stores of a warp are then 128 contiguous bytes. R = the power of two >= dk / 16.
+//
+// Beside it: token_shift (every projection's own blend of a token's input with the previous token's, the previous token of a
+// portion's first token coming from the slot), delta_gates (the delta rule's decay and write strength per head) and
+// head_norm_gate (every head's result divided by its root mean square, times a weight, times silu of a gate).
+#include "common.cuh"
+
+#include <cmath>
+
+namespace {
+
+constexpr int KPT = 16;       // state numbers of a column that one lane holds
+constexpr int LS_THREADS = 128;
+
+__device__ __forceinline__ float parts_sum(const float* __restrict__ p, int n_parts, size_t pstride, size_t i) {
+  float s = p[i];
+  for (int k = 1; k < n_parts; ++k) s += p[(size_t)k * pstride + i];
+  return s;
+}
+
+struct Sums {  // columns off.. of float32 sums [parts, rows, width]
+  const float* p; int n; size_t stride; int width, off;
+};
+
+struct LinearStateParams {
+  Sums q, k, v;
+  const float* decay; int decay_width, decay_off;  // float32 rows: MODE 0/1 a number a (head, key channel); MODE 2 [g: H | beta: H]
+  const float* bonus;                              // MODE 1: [H, dk]
+  float* state;                                    // [slots, H, R * KPT, dv] in the layout above
+  const int* seq_qoff; const int* seq_ntok; const int* seq_slot;
+  float* out;                                      // [tokens, H * dv]
+  int H, G, dk, dv, R, tile;
+  float q_scale, unit_eps;
+};
+
+template <int MODE>
+__global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(const LinearStateParams p) {
+  extern __shared__ float sh_ls[];
+  dep_launch();
+  dep_wait();
+  const int seq = blockIdx.z, head = blockIdx.y, R = p.R, dk = p.dk, dv = p.dv;
+  const int n_tok = p.seq_ntok[seq];
+  if (n_tok <= 0) return;
+  const int first = p.seq_qoff[seq];
+  const int dkp = R * KPT;
+  const int kvh = head / (p.H / p.G);
+  const int lane_r = threadIdx.x & (R - 1);
+  const int col = blockIdx.x * (LS_THREADS / R) + threadIdx.x / R;
+  const bool live = col < dv;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* q_s = sh_ls;                              // [tile][dkp]
+  float* k_s = q_s + (size_t)p.tile * dkp;         // [tile][dkp]
+  float* a_s = k_s + (size_t)p.tile * dkp;         // [tile][dkp] (MODE 0/1) or [tile][2] (MODE 2)
+  float* v_s = a_s + (size_t)p.tile * (MODE == 2 ? 2 : dkp);  // [tile][dv]
+
+  float* st = p.state + ((size_t)p.seq_slot[seq] * p.H + head) * (size_t)dkp * dv;
+  float s[KPT], u[KPT];
+#pragma unroll
+  for (int m = 0; m < KPT; ++m) {
+    s[m] = live ? st[((size_t)m * dv + col) * R + lane_r] : 0.f;
+    const int i = lane_r + R * m;
+    u[m] = (MODE == 1 && i < dk) ? p.bonus[(size_t)head * dk + i] : 0.f;
+  }
+
+  for (int t0 = 0; t0 < n_tok; t0 += p.tile) {
+    const int cnt = min(p.tile, n_tok - t0);
+    __syncthreads();  // the tile before this one has been used up
+    for (int tt = warp; tt < cnt; tt += LS_THREADS / 32) {
+      const size_t row = (size_t)(first + t0 + tt);
+      float ssq = 0.f, ssk = 0.f;
+      for (int i = lane; i < dkp; i += 32) {
+        float qv = 0.f, kv = 0.f, av = 0.f;
+        if (i < dk) {
+          qv = parts_sum(p.q.p, p.q.n, p.q.stride, row * p.q.width + p.q.off + (size_t)kvh * dk + i);
+          kv = parts_sum(p.k.p, p.k.n, p.k.stride, row * p.k.width + p.k.off + (size_t)kvh * dk + i);
+          if (MODE != 2) av = p.decay[row * p.decay_width + p.decay_off + (size_t)head * dk + i];
+        }
+        ssq = fmaf(qv, qv, ssq);
+        ssk = fmaf(kv, kv, ssk);
+        q_s[tt * dkp + i] = qv;
+        k_s[tt * dkp + i] = kv;
+        if (MODE != 2) a_s[tt * dkp + i] = av;
+      }
+      float qmul = p.q_scale, kmul = 1.0f;
+      if (MODE == 2) {
+        ssq = warp_sum(ssq);
+        ssk = warp_sum(ssk);
+        if (p.unit_eps >= 0.f) {
+          qmul = p.q_scale / sqrtf(ssq + p.unit_eps);
+          kmul = 1.0f / sqrtf(ssk + p.unit_eps);
+        }
+        if (lane == 0) {
+          a_s[tt * 2] = p.decay[row * p.decay_width + p.decay_off + head];
+          a_s[tt * 2 + 1] = p.decay[row * p.decay_width + p.decay_off + p.H + head];
+        }
+      }
+      for (int i = lane; i < dkp; i += 32) {  // the lane's own numbers again
+        q_s[tt * dkp + i] *= qmul;
+        if (MODE == 2) k_s[tt * dkp + i] *= kmul;
+      }
+      for (int j = lane; j < dv; j += 32)
+        v_s[tt * dv + j] = parts_sum(p.v.p, p.v.n, p.v.stride, row * p.v.width + p.v.off + (size_t)head * dv + j);
+    }
+    __syncthreads();
+    for (int tt = 0; tt < cnt; ++tt) {
+      const float* qt = q_s + tt * dkp + lane_r;
+      const float* kt = k_s + tt * dkp + lane_r;
+      const float vj = live ? v_s[tt * dv + col] : 0.f;
+      float acc = 0.f;
+      if (MODE == 0) {
+        const float* at = a_s + tt * dkp + lane_r;
+#pragma unroll
+        for (int m = 0; m < KPT; ++m) {
+          s[m] = fmaf(kt[R * m], vj, at[R * m] * s[m]);
+          acc = fmaf(s[m], qt[R * m], acc);
+        }
+      } else if (MODE == 1) {
+        const float* at = a_s + tt * dkp + lane_r;
+#pragma unroll
+        for (int m = 0; m < KPT; ++m) {
+          const float kv = kt[R * m] * vj;
+          acc = fmaf(fmaf(u[m], kv, s[m]), qt[R * m], acc);
+          s[m] = fmaf(at[R * m], s[m], kv);
+        }
+      } else {
+        const float g = a_s[tt * 2], beta = a_s[tt * 2 + 1];
+        float dot = 0.f;
+#pragma unroll
+        for (int m = 0; m < KPT; ++m) {
+          s[m] *= g;
+          dot = fmaf(s[m], kt[R * m], dot);
+        }
+        for (int o = R >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+        const float w = beta * (vj - dot);
+#pragma unroll
+        for (int m = 0; m < KPT; ++m) {
+          s[m] = fmaf(kt[R * m], w, s[m]);
+          acc = fmaf(s[m], qt[R * m], acc);
+        }
+      }
+      for (int o = R >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (live && lane_r == 0) p.out[(size_t)(first + t0 + tt) * p.H * dv + (size_t)head * dv + col] = acc;
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int m = 0; m < KPT; ++m) st[((size_t)m * dv + col) * R + lane_r] = s[m];
+  }
+}
+
+// out[s][t, c] = x[t, c] + (prev[c] - x[t, c]) * mu[s, c], prev = the request's token before t (of this step, or from the slot)
+template <typename T>
+__global__ void token_shift_kernel(const T* __restrict__ x, const float* __restrict__ mu, int n_out, const float* __restrict__ shift_state,
+                                   const int* __restrict__ token_seq, const int* __restrict__ seq_qoff, const int* __restrict__ seq_slot,
+                                   T* __restrict__ out, int n_tokens, int D) {
+  dep_launch();
+  dep_wait();
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= D) return;
+  for (int tok = blockIdx.y; tok < n_tokens; tok += gridDim.y) {
+    const int seq = token_seq[tok];
+    const float cur = to_f32(x[(size_t)tok * D + c]);
+    const float prev = tok > seq_qoff[seq] ? to_f32(x[(size_t)(tok - 1) * D + c]) : shift_state[(size_t)seq_slot[seq] * D + c];
+    const float d = prev - cur;
+    for (int s = 0; s < n_out; ++s) out[((size_t)s * n_tokens + tok) * D + c] = from_f32<T>(fmaf(d, mu[(size_t)s * D + c], cur));
+  }
+}
+
+template <typename T>
+__global__ void token_shift_state_kernel(const T* __restrict__ x, float* __restrict__ shift_state, const int* __restrict__ seq_qoff,
+                                         const int* __restrict__ seq_ntok, const int* __restrict__ seq_slot, int n_seqs, int D) {
+  dep_launch();
+  dep_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)n_seqs * D) return;
+  const int seq = (int)(i / D), c = (int)(i - (size_t)seq * D);
+  const int n = seq_ntok[seq];
+  if (n > 0) shift_state[(size_t)seq_slot[seq] * D + c] = to_f32(x[(size_t)(seq_qoff[seq] + n - 1) * D + c]);
+}
+
+// out[t] = [g: H | beta: H], g = exp(-exp(a_log[h]) * softplus(a[t, h] + dt_bias[h])), beta = sigmoid(b[t, h])
+__global__ void delta_gates_kernel(const Sums a, const Sums b, const float* __restrict__ a_log, const float* __restrict__ dt_bias,
+                                   float* __restrict__ out, int n_tokens, int H) {
+  dep_launch();
+  dep_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)n_tokens * H) return;
+  const size_t tok = i / H;
+  const int h = (int)(i - tok * H);
+  const float z = parts_sum(a.p, a.n, a.stride, tok * a.width + a.off + h) + dt_bias[h];
+  const float sp = z > 20.0f ? z : log1pf(expf(z));
+  out[tok * 2 * H + h] = expf(-expf(a_log[h]) * sp);
+  out[tok * 2 * H + H + h] = 1.0f / (1.0f + expf(-parts_sum(b.p, b.n, b.stride, tok * b.width + b.off + h)));
+}
+
+// a warp a (token, head): out = o / sqrt(mean(o^2) + eps) * weight * silu(gate); weight [dv] for all heads or [H * dv]
+template <typename T>
+__global__ void __launch_bounds__(128)
+    head_norm_gate_kernel(const float* __restrict__ o, const float* __restrict__ weight, int weight_per_head, const Sums gate, float eps,
+                          T* __restrict__ out, int n_tokens, int H, int dv) {
+  dep_launch();
+  dep_wait();
+  const long long item = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+  if (item >= (long long)n_tokens * H) return;
+  const int lane = threadIdx.x & 31;
+  const size_t tok = (size_t)(item / H);
+  const int head = (int)(item - (long long)tok * H);
+  const float* row = o + tok * (size_t)H * dv + (size_t)head * dv;
+  float ss = 0.f;
+  for (int d = lane; d < dv; d += 32) ss = fmaf(row[d], row[d], ss);
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)dv + eps);
+  for (int d = lane; d < dv; d += 32) {
+    float v = row[d] * inv * weight[weight_per_head ? (size_t)head * dv + d : d];
+    if (gate.p) {
+      const float g = parts_sum(gate.p, gate.n, gate.stride, tok * gate.width + gate.off + (size_t)head * dv + d);
+      v *= g / (1.0f + expf(-g));
+    }
+    out[tok * (size_t)H * dv + (size_t)head * dv + d] = from_f32<T>(v);
+  }
+}
+
+int lanes_for(int dk) {
+  int r = 1;
+  while (r * KPT < dk) r *= 2;
+  return r;
+}
+
+}  // namespace
+
+// Lanes a column of the state is spread over (the slot holds lanes * 16 rows a head); 0 if dk is beyond the kernel.
+extern "C" int llm_linear_state_lanes(int dk) {
+  if (dk <= 0 || dk > 32 * KPT) return 0;
+  return lanes_for(dk);
+}
+
+extern "C" int llm_linear_state(int mode, const float* q, int qn, long long qs, int qw, int qo, const float* k, int kn, long long ks, int kw,
+                                int ko, const float* v, int vn, long long vs, int vw, int vo, const float* decay, int decay_width,
+                                int decay_off, const float* bonus, float* state, const int* seq_qoff, const int* seq_ntok,
+                                const int* seq_slot, float* out, int n_seqs, int H, int G, int dk, int dv, float q_scale, float unit_eps,
+                                cudaStream_t stream) {
+  if (n_seqs == 0) return LLM_OK;
+  LLM_REQUIRE(mode >= 0 && mode <= 2, "linear_state: unknown update rule %d", mode);
+  LLM_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && H > 0 && H <= 65535 && G > 0 && H % G == 0 && dv > 0, "linear_state: bad sizes");
+  LLM_REQUIRE(llm_linear_state_lanes(dk) > 0, "linear_state: a key size of %d is not in 1..%d", dk, 32 * KPT);
+  LLM_REQUIRE(mode == 2 || G == H, "linear_state: only the delta rule shares query/key heads");
+  LLM_REQUIRE(q && k && v && decay && state && out && qn >= 1 && kn >= 1 && vn >= 1 && (mode != 1 || bonus), "linear_state: missing tensors");
+  LLM_REQUIRE(qo + G * dk <= qw && ko + G * dk <= kw && vo + H * dv <= vw && decay_off + (mode == 2 ? 2 * H : H * dk) <= decay_width,
+              "linear_state: columns outside their rows");
+  LinearStateParams p;
+  p.q = Sums{q, qn, (size_t)qs, qw, qo}; p.k = Sums{k, kn, (size_t)ks, kw, ko}; p.v = Sums{v, vn, (size_t)vs, vw, vo};
+  p.decay = decay; p.decay_width = decay_width; p.decay_off = decay_off; p.bonus = bonus; p.state = state;
+  p.seq_qoff = seq_qoff; p.seq_ntok = seq_ntok; p.seq_slot = seq_slot; p.out = out;
+  p.H = H; p.G = G; p.dk = dk; p.dv = dv; p.R = lanes_for(dk); p.q_scale = q_scale; p.unit_eps = unit_eps;
+  const int dkp = p.R * KPT;
+  auto smem_for = [&](int tile) { return (size_t)tile * ((mode == 2 ? 2 * dkp + 2 : 3 * dkp) + dv) * sizeof(float); };
+  p.tile = 16;
+  while (p.tile > 1 && smem_for(p.tile) > 48 * 1024) p.tile /= 2;
+  LLM_REQUIRE(smem_for(p.tile) <= 48 * 1024, "linear_state: heads of %d / %d numbers exceed one block's shared memory", dk, dv);
+  dim3 grid(ceil_div(dv, LS_THREADS / p.R), H, n_seqs);
+  if (mode == 0) launch_kernel(linear_state_kernel<0>, grid, LS_THREADS, smem_for(p.tile), stream, p);
+  else if (mode == 1) launch_kernel(linear_state_kernel<1>, grid, LS_THREADS, smem_for(p.tile), stream, p);
+  else launch_kernel(linear_state_kernel<2>, grid, LS_THREADS, smem_for(p.tile), stream, p);
+  LLM_CHECK_LAUNCH("linear_state");
+  return LLM_OK;
+}
+
+extern "C" int llm_token_shift(const void* x, const float* mu, int n_out, float* shift_state, const int* token_seq, const int* seq_qoff,
+                               const int* seq_ntok, const int* seq_slot, void* out, int dtype, int n_tokens, int n_seqs, int D,
+                               cudaStream_t stream) {
+  if (n_tokens == 0) return LLM_OK;
+  LLM_REQUIRE(n_tokens > 0 && n_seqs > 0 && D > 0 && n_out >= 1, "token_shift: bad sizes");
+  LLM_REQUIRE(dtype == LLM_F32 || dtype == LLM_BF16, "token_shift: unknown dtype %d", dtype);
+  dim3 grid(ceil_div(D, 256), n_tokens < 65535 ? n_tokens : 65535);
+  const int sblocks = ceil_div((long long)n_seqs * D, 256);
+  if (dtype == LLM_F32) {
+    launch_kernel(token_shift_kernel<float>, grid, 256, 0, stream, (const float*)x, mu, n_out, (const float*)shift_state, token_seq, seq_qoff,
+                  seq_slot, (float*)out, n_tokens, D);
+    launch_kernel(token_shift_state_kernel<float>, sblocks, 256, 0, stream, (const float*)x, shift_state, seq_qoff, seq_ntok, seq_slot, n_seqs, D);
+  } else {
+    launch_kernel(token_shift_kernel<bf16>, grid, 256, 0, stream, (const bf16*)x, mu, n_out, (const float*)shift_state, token_seq, seq_qoff,
+                  seq_slot, (bf16*)out, n_tokens, D);
+    launch_kernel(token_shift_state_kernel<bf16>, sblocks, 256, 0, stream, (const bf16*)x, shift_state, seq_qoff, seq_ntok, seq_slot, n_seqs, D);
+  }
+  LLM_CHECK_LAUNCH("token_shift");
+  return LLM_OK;
+}
+
+extern "C" int llm_delta_gates(const float* a, int an, long long as, int aw, int ao, const float* b, int bn, long long bs, int bw, int bo,
+                               const float* a_log, const float* dt_bias, float* out, int n_tokens, int H, cudaStream_t stream) {
+  if (n_tokens == 0) return LLM_OK;
+  LLM_REQUIRE(n_tokens > 0 && H > 0 && a && b && a_log && dt_bias && out && an >= 1 && bn >= 1, "delta_gates: bad arguments");
+  LLM_REQUIRE(ao + H <= aw && bo + H <= bw, "delta_gates: columns outside their rows");
+  launch_kernel(delta_gates_kernel, ceil_div((long long)n_tokens * H, 128), 128, 0, stream, Sums{a, an, (size_t)as, aw, ao},
+                Sums{b, bn, (size_t)bs, bw, bo}, a_log, dt_bias, out, n_tokens, H);
+  LLM_CHECK_LAUNCH("delta_gates");
+  return LLM_OK;
+}
+
+extern "C" int llm_head_norm_gate(const float* o, const float* weight, int weight_per_head, const float* gate, int gn, long long gs, int gw,
+                                  int go, float eps, void* out, int dtype, int n_tokens, int H, int dv, cudaStream_t stream) {
+  if (n_tokens == 0) return LLM_OK;
+  LLM_REQUIRE(n_tokens > 0 && H > 0 && dv > 0 && o && weight && out, "head_norm_gate: bad arguments");
+  LLM_REQUIRE(gate == nullptr || (gn >= 1 && go >= 0 && go + H * dv <= gw), "head_norm_gate: gate columns outside the product");
+  const Sums g{gate, gn, (size_t)gs, gw, go};
+  const int blocks = ceil_div((long long)n_tokens * H, 4);
+  if (dtype == LLM_F32)
+    launch_kernel(head_norm_gate_kernel<float>, blocks, 128, 0, stream, o, weight, weight_per_head, g, eps, (float*)out, n_tokens, H, dv);
+  else if (dtype == LLM_BF16)
+    launch_kernel(head_norm_gate_kernel<bf16>, blocks, 128, 0, stream, o, weight, weight_per_head, g, eps, (bf16*)out, n_tokens, H, dv);
+  else
+    LLM_REQUIRE(false, "head_norm_gate: unknown dtype %d", dtype);
+  LLM_CHECK_LAUNCH("head_norm_gate");
+  return LLM_OK;
+}

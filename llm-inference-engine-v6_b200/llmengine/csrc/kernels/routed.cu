@@ -85,7 +85,7 @@ __global__ void route_kernel(const T* __restrict__ x, long long ldx, const T* __
 template <typename T>
 __global__ void route_grouped_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__ wr, const float* __restrict__ correction,
                                      int D, int E, int top, int n_groups, int keep, float norm_eps, int* __restrict__ idx,
-                                     float* __restrict__ share) {
+                                     float* __restrict__ share, int score_mode, int group_top, int normalize) {
   extern __shared__ float sh_r[];  // s[E], choice[E], group score[n_groups]
   float* s = sh_r;
   float* choice = sh_r + E;
@@ -118,29 +118,42 @@ __global__ void route_grouped_kernel(const T* __restrict__ x, long long ldx, con
   }
   __syncthreads();
   if (warp != 0) return;
-  float zmax = -INFINITY;
-  for (int e = lane; e < E; e += 32) zmax = fmaxf(zmax, s[e]);
-  zmax = warp_max(zmax);
-  float sum = 0.f;
-  for (int e = lane; e < E; e += 32) {
-    const float p = expf(s[e] - zmax);
-    s[e] = p;
-    sum += p;
-  }
-  sum = warp_sum(sum);
-  __syncwarp();
-  for (int e = lane; e < E; e += 32) {
-    const float p = s[e] / sum;
-    s[e] = p;
-    choice[e] = p + (correction ? correction[e] : 0.f);
+  if (score_mode == 1) {  // every expert's score by itself: sigmoid of its logit
+    for (int e = lane; e < E; e += 32) {
+      const float p = 1.0f / (1.0f + expf(-s[e]));
+      s[e] = p;
+      choice[e] = p + (correction ? correction[e] : 0.f);
+    }
+  } else {
+    float zmax = -INFINITY;
+    for (int e = lane; e < E; e += 32) zmax = fmaxf(zmax, s[e]);
+    zmax = warp_max(zmax);
+    float sum = 0.f;
+    for (int e = lane; e < E; e += 32) {
+      const float p = expf(s[e] - zmax);
+      s[e] = p;
+      sum += p;
+    }
+    sum = warp_sum(sum);
+    __syncwarp();
+    for (int e = lane; e < E; e += 32) {
+      const float p = s[e] / sum;
+      s[e] = p;
+      choice[e] = p + (correction ? correction[e] : 0.f);
+    }
   }
   __syncwarp();
   const int per = E / n_groups;
   if (keep < n_groups) {
     for (int g = lane; g < n_groups; g += 32) {
-      float best = -INFINITY;
-      for (int e = g * per; e < (g + 1) * per; ++e) best = fmaxf(best, choice[e]);
-      gscore[g] = best;
+      // the group's largest choice score, or (group_top 2) the sum of its two largest
+      float best = -INFINITY, second = -INFINITY;
+      for (int e = g * per; e < (g + 1) * per; ++e) {
+        const float v = choice[e];
+        if (v > best) { second = best; best = v; }
+        else if (v > second) second = v;
+      }
+      gscore[g] = (group_top >= 2 && per >= 2) ? best + second : best;
     }
     __syncwarp();
     // a group stays if fewer than `keep` groups come before it (larger score, or the same score and a lower index)
@@ -177,7 +190,7 @@ __global__ void route_grouped_kernel(const T* __restrict__ x, long long ldx, con
     }
     __syncwarp();
   }
-  if (lane < top) share[(size_t)tok * top + lane] /= (total + norm_eps);
+  if (normalize && lane < top) share[(size_t)tok * top + lane] /= (total + norm_eps);
 }
 
 // One block. counts -> tiles per expert -> scatter. The order of an expert's rows depends on timing;
@@ -310,8 +323,12 @@ extern "C" int llm_route(const void* x, long long ldx, const void* wr, const flo
 }
 
 extern "C" int llm_route_grouped(const void* x, long long ldx, const void* wr, const float* correction, int n_tokens, int D, int E, int top,
-                                 int n_groups, int keep, float norm_eps, int* idx, float* share, int dtype, cudaStream_t stream) {
+                                 int n_groups, int keep, float norm_eps, int* idx, float* share, int dtype, int score_mode, int group_top, int normalize,
+                                 cudaStream_t stream) {
+  // score_mode 0: softmax over all experts, 1: sigmoid of each logit; group_top: a group's score is its largest choice score (1) or
+  // the sum of its two largest (2); normalize 0: the chosen experts' scores are the weights as they are
   if (n_tokens == 0) return LLM_OK;
+  LLM_REQUIRE((score_mode == 0 || score_mode == 1) && (group_top == 1 || group_top == 2), "route: unknown score mode %d or group score over %d", score_mode, group_top);
   LLM_REQUIRE(n_tokens > 0 && D > 0 && E > 0 && top > 0 && top <= E, "route: bad sizes experts=%d top=%d", E, top);
   LLM_REQUIRE(top <= 32 && E <= 4096, "route: at most 32 of 4096 experts a token (got %d of %d)", top, E);
   LLM_REQUIRE(n_groups >= 1 && keep >= 1 && keep <= n_groups && E % n_groups == 0, "route: %d experts do not form %d equal groups of which %d stay", E, n_groups, keep);
@@ -319,10 +336,10 @@ extern "C" int llm_route_grouped(const void* x, long long ldx, const void* wr, c
   const size_t smem = (size_t)(2 * E + n_groups) * sizeof(float);
   if (dtype == LLM_F32)
     launch_kernel(route_grouped_kernel<float>, n_tokens, 256, smem, stream, (const float*)x, ldx, (const float*)wr, correction, D, E, top, n_groups,
-                  keep, norm_eps, idx, share);
+                  keep, norm_eps, idx, share, score_mode, group_top, normalize);
   else if (dtype == LLM_BF16)
     launch_kernel(route_grouped_kernel<bf16>, n_tokens, 256, smem, stream, (const bf16*)x, ldx, (const bf16*)wr, correction, D, E, top, n_groups,
-                  keep, norm_eps, idx, share);
+                  keep, norm_eps, idx, share, score_mode, group_top, normalize);
   else
     LLM_REQUIRE(false, "route: unknown dtype %d", dtype);
   LLM_CHECK_LAUNCH("route_grouped");

@@ -94,20 +94,29 @@ __global__ void conv_state_kernel(const float* __restrict__ parts, int n_parts, 
 
 constexpr int DT_THREADS = 128;
 
+// The low-rank map's two ends. in_act 1: tanh of the low-rank numbers before the map. out_act 0: softplus(z) (a step size);
+// 1: sigmoid(z)^(1/p) = exp(-softplus(-z) / p) (a decay in (0, 1), p its temperature); 2: exp(-exp(z)) (a decay in (0, 1)).
+__device__ __forceinline__ float low_in(float v, int in_act) { return in_act == 1 ? tanhf(v) : v; }
+__device__ __forceinline__ float low_out(float z, int out_act, float p) {
+  if (out_act == 1) return expf(-(z < -20.0f ? -z : log1pf(expf(-z))) / p);
+  if (out_act == 2) return expf(-expf(z));
+  return z > 20.0f ? z : log1pf(expf(z));
+}
+
 // wt: the step-size map stored [R, C] (transposed when loaded), so that neighbouring channels read neighbouring words.
 // A block: 128 channels x TOK tokens; the tokens' low-rank rows lie in shared memory as [R][TOK], so that one 16-byte read
 // feeds four multiply-adds.
 template <typename T, int TOK>
 __global__ void __launch_bounds__(DT_THREADS)
     dt_softplus_kernel(const float* __restrict__ proj, long long ld, int R, const T* __restrict__ wt, const float* __restrict__ bias, int C,
-                       float* __restrict__ dt, int n_tokens) {
+                       float* __restrict__ dt, int n_tokens, int in_act, int out_act, float param) {
   extern __shared__ __align__(16) float low[];  // [R][TOK]
   dep_launch();
   dep_wait();
   const int t0 = blockIdx.y * TOK;
   for (int i = threadIdx.x; i < TOK * R; i += blockDim.x) {
     const int tl = i / R, r = i - tl * R;
-    low[r * TOK + tl] = t0 + tl < n_tokens ? proj[(size_t)(t0 + tl) * ld + r] : 0.f;
+    low[r * TOK + tl] = t0 + tl < n_tokens ? low_in(proj[(size_t)(t0 + tl) * ld + r], in_act) : 0.f;
   }
   __syncthreads();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
@@ -133,8 +142,7 @@ __global__ void __launch_bounds__(DT_THREADS)
   for (int i = 0; i < TOK; ++i) {
     const int t = t0 + i;
     if (t < n_tokens) {
-      const float z = acc[i] + b;
-      dt[(size_t)t * C + c] = z > 20.0f ? z : log1pf(expf(z));
+      dt[(size_t)t * C + c] = low_out(acc[i] + b, out_act, param);
     }
   }
 }
@@ -144,7 +152,7 @@ __global__ void __launch_bounds__(DT_THREADS)
 template <typename T>
 __global__ void __launch_bounds__(128)
     dt_softplus_few_kernel(const float* __restrict__ proj, long long ld, int R, const T* __restrict__ wt, const float* __restrict__ bias, int C,
-                           float* __restrict__ dt, int n_tokens) {
+                           float* __restrict__ dt, int n_tokens, int in_act, int out_act, float param) {
   extern __shared__ __align__(16) float sm_few[];  // low [R][8], then quarters [4][32][8]
   float* low = sm_few;
   float* quarter = sm_few + (size_t)R * 8;
@@ -154,7 +162,7 @@ __global__ void __launch_bounds__(128)
 #pragma unroll 4
   for (int i = threadIdx.x; i < 8 * R; i += 128) {
     const int tl = i / R, r = i - tl * R;
-    low[r * 8 + tl] = t0 + tl < n_tokens ? proj[(size_t)(t0 + tl) * ld + r] : 0.f;
+    low[r * 8 + tl] = t0 + tl < n_tokens ? low_in(proj[(size_t)(t0 + tl) * ld + r], in_act) : 0.f;
   }
   __syncthreads();
   const int lane = threadIdx.x & 31, part = threadIdx.x >> 5;
@@ -180,7 +188,7 @@ __global__ void __launch_bounds__(128)
     const int t = t0 + i;
     if (t < n_tokens) {
       const float z = ((quarter[lane * 8 + i] + quarter[(32 + lane) * 8 + i]) + quarter[(64 + lane) * 8 + i]) + quarter[(96 + lane) * 8 + i] + b;
-      dt[(size_t)t * C + c] = z > 20.0f ? z : log1pf(expf(z));
+      dt[(size_t)t * C + c] = low_out(z, out_act, param);
     }
   }
 }
@@ -379,9 +387,12 @@ extern "C" int llm_conv_silu(const float* parts, int n_parts, long long pstride,
   return LLM_OK;
 }
 
-extern "C" int llm_dt_softplus(const float* proj, long long ld, int R, const void* wt, const float* bias, int C, float* dt, int dtype,
-                               int n_tokens, cudaStream_t stream) {
+// dt[t, c] = out_act(bias[c] + sum_r wt[r, c] * in_act(proj[t, r])): the step-size map of the selective scan (in_act 0, out_act 0) and
+// the decay maps of the linear-state mixers (low_in / low_out above)
+extern "C" int llm_lowrank_map(const float* proj, long long ld, int R, const void* wt, const float* bias, int C, float* dt, int dtype,
+                               int n_tokens, int in_act, int out_act, float param, cudaStream_t stream) {
   if (n_tokens == 0) return LLM_OK;
+  LLM_REQUIRE((in_act == 0 || in_act == 1) && out_act >= 0 && out_act <= 2 && (out_act != 1 || param > 0.f), "lowrank_map: unknown activation %d / %d", in_act, out_act);
   LLM_REQUIRE(n_tokens > 0 && R > 0 && C > 0 && R <= ld, "dt_softplus: bad sizes");
   LLM_REQUIRE(dtype == LLM_F32 || dtype == LLM_BF16, "dt_softplus: unknown dtype %d", dtype);
   if (n_tokens <= 8) {  // single decoded tokens
@@ -389,9 +400,9 @@ extern "C" int llm_dt_softplus(const float* proj, long long ld, int R, const voi
     LLM_REQUIRE(smem_few <= 48 * 1024, "dt_softplus: a step-size rank of %d exceeds one block's shared memory", R);
     dim3 grid_few(ceil_div(C, 32), ceil_div(n_tokens, 8));
     if (dtype == LLM_F32)
-      launch_kernel(dt_softplus_few_kernel<float>, grid_few, 128, smem_few, stream, proj, ld, R, (const float*)wt, bias, C, dt, n_tokens);
+      launch_kernel(dt_softplus_few_kernel<float>, grid_few, 128, smem_few, stream, proj, ld, R, (const float*)wt, bias, C, dt, n_tokens, in_act, out_act, param);
     else
-      launch_kernel(dt_softplus_few_kernel<bf16>, grid_few, 128, smem_few, stream, proj, ld, R, (const bf16*)wt, bias, C, dt, n_tokens);
+      launch_kernel(dt_softplus_few_kernel<bf16>, grid_few, 128, smem_few, stream, proj, ld, R, (const bf16*)wt, bias, C, dt, n_tokens, in_act, out_act, param);
     LLM_CHECK_LAUNCH("dt_softplus");
     return LLM_OK;
   }
@@ -401,11 +412,16 @@ extern "C" int llm_dt_softplus(const float* proj, long long ld, int R, const voi
   const int threads = DT_THREADS;
   dim3 grid(ceil_div(C, threads), ceil_div(n_tokens, tok));
   LLM_REQUIRE(grid.y <= 65535, "dt_softplus: too many tokens in one step (%d)", n_tokens);
-#define LLM_DT(T, TOK) launch_kernel(dt_softplus_kernel<T, TOK>, grid, threads, smem, stream, proj, ld, R, (const T*)wt, bias, C, dt, n_tokens)
+#define LLM_DT(T, TOK) launch_kernel(dt_softplus_kernel<T, TOK>, grid, threads, smem, stream, proj, ld, R, (const T*)wt, bias, C, dt, n_tokens, in_act, out_act, param)
   if (dtype == LLM_F32) LLM_DT(float, 32); else LLM_DT(bf16, 32);
 #undef LLM_DT
   LLM_CHECK_LAUNCH("dt_softplus");
   return LLM_OK;
+}
+
+extern "C" int llm_dt_softplus(const float* proj, long long ld, int R, const void* wt, const float* bias, int C, float* dt, int dtype,
+                               int n_tokens, cudaStream_t stream) {
+  return llm_lowrank_map(proj, ld, R, wt, bias, C, dt, dtype, n_tokens, 0, 0, 0.f, stream);
 }
 
 extern "C" int llm_selective_scan_piece() { return SCAN_CHUNK; }

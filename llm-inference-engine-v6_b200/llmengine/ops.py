@@ -216,7 +216,15 @@ class CudaOps:
                                          _stream()), lib)
         return h
 
-    ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}  # what a gated feed-forward may apply to its gate
+    # what a gated feed-forward may apply to its gate; "clamped_swish" comes as ("clamped_swish", limit, slope):
+    # g <- min(g, limit), u <- clamp(u, -limit, limit), g * sigmoid(slope * g) * (u + 1)
+    ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "clamped_swish": 2}
+
+    @classmethod
+    def _act_args(cls, act):
+        if isinstance(act, tuple):
+            return c_int(cls.ACTIVATIONS[act[0]]), c_float(act[1]), c_float(act[2])
+        return c_int(cls.ACTIVATIONS[act]), c_float(0.0), c_float(1.0)
 
     def silu_mul(self, gate_up: torch.Tensor, out: torch.Tensor, block: int = 0, act: str = "silu") -> torch.Tensor:
         """gate_up [n, 2*ff] -> out [n, ff] = act(gate)*up. block 0: gate columns first, then up;
@@ -226,7 +234,7 @@ class CudaOps:
         n, ff = out.shape
         assert gate_up.is_contiguous() and out.is_contiguous() and gate_up.shape == (n, 2 * ff)
         self._check(lib.llm_silu_mul(_ptr(gate_up), _ptr(out), c_int(dtype_code(out.dtype)), c_int(n), c_int(ff),
-                                     c_int(block), c_int(self.ACTIVATIONS[act]), _stream()), lib)
+                                     c_int(block), *self._act_args(act), _stream()), lib)
         return out
 
     EPILOGUE_ACTIVATIONS = ("silu", "gelu_tanh")  # what the gate|up product applies in its own epilogue (gemm_swiglu)
@@ -527,7 +535,7 @@ class CudaOps:
         lib = self.lib()
         self._check(lib.llm_silu_mul_partials(_ptr(parts), c_int(parts.shape[0]), c_longlong(parts.stride(0)), _ptr(out),
                                               c_int(dtype_code(out.dtype)), c_int(n), c_int(ff), c_int(block),
-                                              *_row_scale_args(row_scale), c_int(self.ACTIVATIONS[act]), _stream()), lib)
+                                              *_row_scale_args(row_scale), *self._act_args(act), _stream()), lib)
         return out
 
     def tensor_core_error(self) -> int:
@@ -951,10 +959,13 @@ class CudaOps:
     ROUTED_EPILOGUES = {"gelu": 0, "share": 1, "silu_pairs": 2}
 
     def route_grouped(self, x: torch.Tensor, w: torch.Tensor, correction: Optional[torch.Tensor], top: int, groups: int, keep: int,
-                      norm_eps: float, idx: torch.Tensor, share: torch.Tensor) -> None:
-        """Per token: s = softmax(w x) over all experts (float32); choice = s + correction; only experts of the `keep` of
-        `groups` equal groups of neighbours with the largest choice scores can be chosen; idx [n, top] = the largest choice
-        scores among them (the lower index wins a tie); share [n, top] = their s divided by (the sum of the chosen s + norm_eps)."""
+                      norm_eps: float, idx: torch.Tensor, share: torch.Tensor, score: str = "softmax", group_top: int = 1,
+                      normalize: bool = True) -> None:
+        """Per token: s = softmax(w x) over all experts, or (score "sigmoid") the sigmoid of every logit (float32); choice = s +
+        correction; only experts of the `keep` of `groups` equal groups of neighbours with the largest group scores can be chosen
+        (a group's score: its largest choice score, or with group_top 2 the sum of its two largest; the others count as minus
+        infinity); idx [n, top] = the largest choice scores among them (the lower index wins a tie); share [n, top] = their s
+        divided by (the sum of the chosen s + norm_eps), or as they are (normalize False)."""
         _need(x, "route.x"); _need(w, "route.w", x.dtype); _need(idx, "route.idx", torch.int32); _need(share, "route.share", torch.float32)
         n, D = x.shape
         E = w.shape[0]
@@ -966,7 +977,8 @@ class CudaOps:
         lib = self.lib()
         self._check(lib.llm_route_grouped(_ptr(x), c_longlong(x.stride(0)), _ptr(w), _ptr(correction), c_int(n), c_int(D), c_int(E),
                                           c_int(top), c_int(groups), c_int(keep), c_float(norm_eps), _ptr(idx), _ptr(share),
-                                          c_int(dtype_code(x.dtype)), _stream()), lib)
+                                          c_int(dtype_code(x.dtype)), c_int({"softmax": 0, "sigmoid": 1}[score]), c_int(group_top),
+                                          c_int(1 if normalize else 0), _stream()), lib)
 
     def routed_tile_rows(self, n_tokens: int = 0, dtype: Optional[torch.dtype] = None, inner=(), per_expert: float = 0.0) -> int:
         """Rows of a tile of the per-expert products: the tensor-core kernel's in bfloat16 when every product's inner
@@ -1094,12 +1106,13 @@ class CudaOps:
 
     def gated_attention(self, q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, batch, block_table: torch.Tensor,
                         out: torch.Tensor, nq: int, nkv: int, dk: int, dv: int, scale: float, window: int = 0, chunk: int = 0,
-                        sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, gate_off: int = 0) -> torch.Tensor:
+                        sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, gate_off: int = 0,
+                        gate_per_head: bool = False) -> torch.Tensor:
         """Causal attention of every token of the step over the cache positions of its request from the later of the window's
         and the chunk's start (chunks are [c * chunk, (c + 1) * chunk) in absolute positions; 0: none) up to its own; keys of dk
         and values of dv numbers a head; sink (float32 [nq], optional): exp(sink[head]) is one more term of the softmax's
         denominator; gate (float32 partial sums [p, n, width], optional): the result times sigmoid(sum_p gate[p, t, gate_off +
-        head * dv + d]). q rows of [nq * dk]; out [n, nq * dv]."""
+        head * dv + d]), or with gate_per_head one gate a head at column gate_off + head. q rows of [nq * dk]; out [n, nq * dv]."""
         _need(q, "attention.q"); _need(kcache, "attention.kcache", q.dtype); _need(vcache, "attention.vcache", q.dtype)
         _need(out, "attention.out", q.dtype); _need(block_table, "attention.block_table", torch.int32)
         assert kcache.is_contiguous() and vcache.is_contiguous() and block_table.is_contiguous()
@@ -1128,8 +1141,8 @@ class CudaOps:
                     _ptr(q), c_longlong(q.stride(0)), _ptr(kcache), _ptr(vcache), _ptr(batch.seq_start), _ptr(batch.seq_ntok), _ptr(batch.seq_qoff),
                     _ptr(block_table), c_int(block_table.shape[1]), _ptr(out), c_longlong(out.stride(0)), c_int(batch.n_seqs),
                     c_int(batch.max_new_tokens), c_int(nq), c_int(nkv), c_int(dk), c_int(dv), c_int(page), c_float(scale), c_int(window),
-                    c_int(chunk), _ptr(sink), _ptr(gate), c_int(gp), c_longlong(gs), c_int(gw), c_int(gate_off), c_int(batch.n_tokens),
-                    c_int(n_splits), c_int(split_keys), _ptr(scratch), _stream()), lib)
+                    c_int(chunk), _ptr(sink), _ptr(gate), c_int(gp), c_longlong(gs), c_int(gw), c_int(gate_off), c_int(1 if gate_per_head else 0),
+                    c_int(batch.n_tokens), c_int(n_splits), c_int(split_keys), _ptr(scratch), _stream()), lib)
                 if n_splits > 1:
                     self.launches += 1  # the kernel that merges the pieces
                 return out
@@ -1139,7 +1152,7 @@ class CudaOps:
                                                  c_int(block_table.shape[1]), _ptr(out), c_longlong(out.stride(0)), c_int(batch.n_tokens),
                                                  c_int(nq), c_int(nkv), c_int(dk), c_int(dv), c_int(page), c_float(scale), c_int(window),
                                                  c_int(chunk), _ptr(sink), _ptr(gate), c_int(gp), c_longlong(gs), c_int(gw), c_int(gate_off),
-                                                 _stream()), lib)
+                                                 c_int(1 if gate_per_head else 0), _stream()), lib)
         return out
 
     def gated_attention_kernel(self, nq: int, nkv: int, dk: int, dv: int) -> str:
@@ -1229,6 +1242,133 @@ class CudaOps:
         return out
 
     SCAN_PIECES_FROM = 192  # tokens of the step's longest portion from which the scan runs in pieces
+
+    LOWRANK_OUT = {"softplus": 0, "sigmoid_root": 1, "exp_neg_exp": 2}
+
+    def lowrank_map(self, proj: torch.Tensor, rank: int, weight_t: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor,
+                    n_tokens: int, in_act: Optional[str] = None, out_act: str = "softplus", param: float = 0.0) -> torch.Tensor:
+        """out[t, c] (float32) = g(bias[c] + sum_r weight_t[r, c] * f(proj[t, r])) for the first `rank` columns of the float32 rows
+        proj; weight_t [rank, channels]. f: None or "tanh". g: "softplus"; "sigmoid_root": sigmoid(z)^(1 / param); "exp_neg_exp":
+        exp(-exp(z)). dt_softplus is this map with f None and g softplus."""
+        _need(proj, "lowrank.proj", torch.float32); _need(weight_t, "lowrank.weight"); _need(out, "lowrank.out", torch.float32)
+        C = weight_t.shape[1]
+        assert weight_t.is_contiguous() and weight_t.shape[0] == rank and out.is_contiguous() and out.shape[1] == C and out.shape[0] >= n_tokens
+        assert in_act in (None, "tanh")
+        if bias is not None:
+            _need(bias, "lowrank.bias", torch.float32)
+            assert bias.numel() == C
+        lib = self.lib()
+        self._check(lib.llm_lowrank_map(_ptr(proj), c_longlong(proj.stride(0)), c_int(rank), _ptr(weight_t), _ptr(bias), c_int(C), _ptr(out),
+                                        c_int(dtype_code(weight_t.dtype)), c_int(n_tokens), c_int(1 if in_act == "tanh" else 0),
+                                        c_int(self.LOWRANK_OUT[out_act]), c_float(param), _stream()), lib)
+        return out
+
+    # ------------------------------------------------------------------ two branches into one
+    def pair_combine(self, a: torch.Tensor, b: torch.Tensor, wa: Optional[torch.Tensor], wb: Optional[torch.Tensor], ca: float, cb: float,
+                     eps: float, out: torch.Tensor, n_rows: Optional[int] = None) -> torch.Tensor:
+        """out[:n] (float32 [n, dim]) = ca * f(a) + cb * f(b) for two sets of float32 sums ([n, dim] or [parts, n, dim], added in index
+        order); with a weight (float32 [dim]) f is the row divided by its root mean square (eps inside the root) times the weight,
+        without one the identity."""
+        n = out.shape[0] if n_rows is None else n_rows
+        dim = out.shape[1]
+        args = []
+        for t, name in ((a, "a"), (b, "b")):
+            _need(t, "pair_combine." + name, torch.float32)
+            assert t.is_contiguous() and t.shape[-1] == dim and t.shape[-2] >= n
+            args += [_ptr(t), c_int(t.shape[0] if t.dim() == 3 else 1), c_longlong(t.stride(0) if t.dim() == 3 else 0)]
+        for w in (wa, wb):
+            if w is not None:
+                _need(w, "pair_combine.weight", torch.float32)
+                assert w.numel() == dim
+        _need(out, "pair_combine.out", torch.float32)
+        assert out.is_contiguous()
+        lib = self.lib()
+        self._check(lib.llm_pair_combine(*args, _ptr(wa), _ptr(wb), c_float(ca), c_float(cb), c_float(eps), _ptr(out), c_int(n), c_int(dim),
+                                         _stream()), lib)
+        return out
+
+    # ------------------------------------------------------------------ mixers with a matrix of state per head
+    LINEAR_STATE_RULES = {"decay_write_read": 0, "bonus_read_decay_write": 1, "delta": 2}
+
+    def linear_state_shape(self, heads: int, dk: int, dv: int):
+        """Shape of the float32 state that linear_state keeps per request (its layout is the kernel's own)."""
+        if not 1 <= dk <= 512:
+            raise ValueError(f"linear state: a key size of {dk} is beyond the kernel (1..512)")
+        lanes = 1  # a column's dk numbers lie on `lanes` lanes of a warp, 16 a lane (llm_linear_state_lanes)
+        while lanes * 16 < dk:
+            lanes *= 2
+        return (heads, lanes * 16, dv)
+
+    @staticmethod
+    def _sums(t: torch.Tensor, off: int, name: str):
+        """(pointer, parts, stride between parts, row width, column offset) of float32 sums [parts, n, width] or rows [n, width]."""
+        _need(t, name, torch.float32)
+        assert t.is_contiguous() and t.dim() in (2, 3)
+        return [_ptr(t), c_int(t.shape[0] if t.dim() == 3 else 1), c_longlong(t.stride(0) if t.dim() == 3 else 0), c_int(t.shape[-1]), c_int(off)]
+
+    def linear_state(self, rule: str, q, q_off: int, k, k_off: int, v, v_off: int, decay: torch.Tensor, decay_off: int,
+                     bonus: Optional[torch.Tensor], state: torch.Tensor, batch, out: torch.Tensor, heads: int, kv_heads: int, dk: int,
+                     dv: int, q_scale: float = 1.0, unit_eps: float = -1.0) -> torch.Tensor:
+        """Token after token of every request, per head a matrix S [dk, dv] (float32, in the request's slot of `state`):
+        "decay_write_read": S <- diag(a) S + k v^T, o = S^T q; "bonus_read_decay_write": o = (S + diag(bonus) k v^T)^T q, then
+        S <- diag(a) S + k v^T; "delta": S <- g S, w = beta (v - S^T k), S <- S + k w^T, o = S^T q with q and k made unit vectors
+        per head first (x / sqrt(sum x^2 + unit_eps); unit_eps < 0: as they are). q is multiplied by q_scale. q, k, v: float32 sums
+        ([parts, n, width] or [n, width]) read at column offsets, q and k with kv_heads heads of dk (head h reads head
+        h // (heads / kv_heads)), v with heads of dv. decay: float32 rows; at decay_off a number per (head, key channel), or for
+        "delta" [g: heads | beta: heads]. out float32 [n, heads * dv]."""
+        _need(decay, "linear_state.decay", torch.float32); _need(state, "linear_state.state", torch.float32); _need(out, "linear_state.out", torch.float32)
+        assert decay.is_contiguous() and decay.dim() == 2 and state.is_contiguous() and out.is_contiguous() and out.shape[1] == heads * dv
+        assert tuple(state.shape[1:]) == tuple(self.linear_state_shape(heads, dk, dv))
+        if bonus is not None:
+            _need(bonus, "linear_state.bonus", torch.float32)
+            assert bonus.is_contiguous() and bonus.numel() == heads * dk
+        lib = self.lib()
+        self._check(lib.llm_linear_state(c_int(self.LINEAR_STATE_RULES[rule]), *self._sums(q, q_off, "linear_state.q"),
+                                         *self._sums(k, k_off, "linear_state.k"), *self._sums(v, v_off, "linear_state.v"), _ptr(decay),
+                                         c_int(decay.shape[1]), c_int(decay_off), _ptr(bonus), _ptr(state), _ptr(batch.seq_qoff),
+                                         _ptr(batch.seq_ntok), _ptr(batch.seq_slot), _ptr(out), c_int(batch.n_seqs), c_int(heads),
+                                         c_int(kv_heads), c_int(dk), c_int(dv), c_float(q_scale), c_float(unit_eps), _stream()), lib)
+        return out
+
+    def token_shift(self, x: torch.Tensor, mu: torch.Tensor, shift_state: torch.Tensor, batch, out: torch.Tensor) -> torch.Tensor:
+        """out[s, t] = x[t] + (x[t - 1] - x[t]) * mu[s] for every blend s (mu float32 [blends, dim]), t - 1 the request's token before t:
+        of this step, or for a portion's first token the row kept in shift_state [slots, dim] (float32), which afterwards holds the
+        request's last row."""
+        _need(x, "token_shift.x"); _need(mu, "token_shift.mu", torch.float32); _need(shift_state, "token_shift.state", torch.float32)
+        _need(out, "token_shift.out", x.dtype)
+        n, D = batch.n_tokens, x.shape[1]
+        assert x.is_contiguous() and mu.is_contiguous() and mu.shape[1] == D and shift_state.is_contiguous() and shift_state.shape[1] == D
+        assert out.is_contiguous() and tuple(out.shape) == (mu.shape[0], n, D) and x.shape[0] >= n
+        lib = self.lib()
+        self._check(lib.llm_token_shift(_ptr(x), _ptr(mu), c_int(mu.shape[0]), _ptr(shift_state), _ptr(batch.token_seq), _ptr(batch.seq_qoff),
+                                        _ptr(batch.seq_ntok), _ptr(batch.seq_slot), _ptr(out), c_int(dtype_code(x.dtype)), c_int(n),
+                                        c_int(batch.n_seqs), c_int(D), _stream()), lib)
+        self.launches += 1  # the kernel that renews the slot
+        return out
+
+    def delta_gates(self, a, a_off: int, b, b_off: int, a_log: torch.Tensor, dt_bias: torch.Tensor, out: torch.Tensor, n_tokens: int) -> torch.Tensor:
+        """out[t] (float32 [n, 2 heads]) = [exp(-exp(a_log) * softplus(a[t] + dt_bias)) | sigmoid(b[t])]; a, b: float32 sums read
+        at column offsets, a number a head."""
+        H = a_log.numel()
+        _need(a_log, "delta_gates.a_log", torch.float32); _need(dt_bias, "delta_gates.dt_bias", torch.float32); _need(out, "delta_gates.out", torch.float32)
+        assert dt_bias.numel() == H and out.is_contiguous() and out.shape[1] == 2 * H and out.shape[0] >= n_tokens
+        lib = self.lib()
+        self._check(lib.llm_delta_gates(*self._sums(a, a_off, "delta_gates.a"), *self._sums(b, b_off, "delta_gates.b"), _ptr(a_log),
+                                        _ptr(dt_bias), _ptr(out), c_int(n_tokens), c_int(H), _stream()), lib)
+        return out
+
+    def head_norm_gate(self, o: torch.Tensor, weight: torch.Tensor, gate, gate_off: int, eps: float, out: torch.Tensor, n_tokens: int,
+                       heads: int, dv: int) -> torch.Tensor:
+        """out[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * weight * silu(gate[t, h]) per head of dv numbers; o float32
+        [n, heads * dv]; weight float32 [dv] (one for all heads) or [heads * dv]; gate: float32 sums read at gate_off (None: no gate)."""
+        _need(o, "head_norm_gate.o", torch.float32); _need(weight, "head_norm_gate.weight", torch.float32); _need(out, "head_norm_gate.out")
+        assert o.is_contiguous() and out.is_contiguous() and o.shape[1] == heads * dv and out.shape[1] == heads * dv
+        assert weight.numel() in (dv, heads * dv) and weight.is_contiguous()
+        g = self._sums(gate, gate_off, "head_norm_gate.gate") if gate is not None else [c_void_p(0), c_int(0), c_longlong(0), c_int(0), c_int(0)]
+        lib = self.lib()
+        self._check(lib.llm_head_norm_gate(_ptr(o), _ptr(weight), c_int(1 if (weight.numel() == heads * dv and heads > 1) else 0), *g, c_float(eps),
+                                           _ptr(out), c_int(dtype_code(out.dtype)), c_int(n_tokens), c_int(heads), c_int(dv), _stream()), lib)
+        return out
 
     # ------------------------------------------------------------------ sampling
     def sample_scratch_words(self, n_rows: int, vocab: int) -> int:

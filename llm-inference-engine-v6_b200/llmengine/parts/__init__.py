@@ -1,5 +1,6 @@
 """Parts a layer is put together from: mixers, feed-forwards, norms, position encodings, blocks."""
-from . import attention, block, embedding, gated_attention, latent_attention, mlp, norm, position, routed_mlp, selective_scan, token_side  # noqa: F401  (registers the built-in parts)
+from . import (attention, block, embedding, gated_attention, latent_attention, linear_state, mixer_pair, mlp, norm, position, routed_mlp,
+               selective_scan, token_side)  # noqa: F401  (registers the built-in parts)
 from .base import (Block, BuildEnv, Embedding, FeedForward, Head, KVNeed, LayerCache, Mixer, Norm, NormalizedRows,
                    Part, PositionEncoding, Residual, StateNeed, TokenInput)
 from .registry import build_part, part_class, register_part

@@ -165,6 +165,17 @@ def add_into_stream_or_partials(ops, x: torch.Tensor, w: torch.Tensor, ctx, few:
     return ops.gemm_partials(x, w, ctx.ws, tag)
 
 
+def project_sums(ops, ctx, x: torch.Tensor, w: torch.Tensor, tag: str) -> torch.Tensor:
+    """x . w^T as float32 sums [parts, n, out] for consumers that add the parts where they read them: K-split parts for steps of
+    few tokens, one part (the product's float32 results) otherwise."""
+    n = ctx.n_tokens
+    if n <= 64:
+        return ops.gemm_partials(x[:n], w, ctx.ws, tag)
+    sums = ctx.ws.get(tag, (1, n, w.shape[0]), torch.float32)
+    ops.gemm(x[:n], w, sums[0], ctx.ws)
+    return sums
+
+
 def res_sumsq_off(res) -> None:
     if res is not None:  # a delta is on its way: what was left beside the stream no longer describes it
         res.sumsq = res.prescaled = res.prescaled_weight = None

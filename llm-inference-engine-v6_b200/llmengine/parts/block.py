@@ -3,7 +3,9 @@
 "parallel": h += mixer(norm1(h)) + feed_forward(norm2(h)), both norms of the same h; then an optional
 input from the tokens themselves, h += token_input(h).
 "post_norm": the sub-layers read h itself and the norms sit on their outputs, each followed by an optional per-column
-layer scale: h += scale1 * norm1(mixer(h)); h += scale2 * norm2(feed_forward(h))."""
+layer scale: h += scale1 * norm1(mixer(h)); h += scale2 * norm2(feed_forward(h)).
+"sandwich": a norm before and one after each sub-layer, and one multiplier on everything that is added:
+h += m * norm1_out(mixer(norm1(h))); h += m * norm2_out(feed_forward(norm2(h)))."""
 from __future__ import annotations
 
 from typing import List
@@ -197,6 +199,75 @@ class PostNormBlock(Block):
         return res
 
 
+class SandwichBlock(Block):
+    """h += m * norm1_out(mixer(norm1(h))); h += m * norm2_out(feed_forward(norm2(h))). The norms before the sub-layers are the
+    framework's norm kernel on the float32 stream; the norms on the results (of the form weight * y / rms(y)) run in the kernel
+    that takes a sub-layer's float32 sums, normalises, multiplies by m and adds into the stream, the row in registers."""
+
+    def __init__(self, spec: BlockSpec, env):
+        super().__init__(spec, env)
+        if spec.norm1_out is None or (spec.feed_forward is not None and (spec.norm2 is None or spec.norm2_out is None)):
+            raise ValueError("a sandwich block needs a norm before and after each of its sub-layers")
+        self.norm1 = build_part("norm", spec.norm1, env)
+        self.mixer = build_part("mixer", spec.mixer, env)
+        self.norm1_out = build_part("norm", spec.norm1_out, env)
+        self.feed_forward = self.norm2 = self.norm2_out = None
+        if spec.feed_forward is not None:
+            self.norm2 = build_part("norm", spec.norm2, env)
+            self.feed_forward = build_part("feed_forward", spec.feed_forward, env)
+            self.norm2_out = build_part("norm", spec.norm2_out, env)
+        for norm in (self.norm1_out, self.norm2_out):
+            if norm is not None and type(norm).prescale_weight is Norm.prescale_weight:
+                raise ValueError("a sandwich block needs norms of the form weight * y / rms(y) on its sub-layers' results")
+        self.mult = None
+
+    def _subs(self):
+        spec = self.spec
+        subs = [("norm", spec.norm1), ("mixer", spec.mixer), ("norm", spec.norm1_out)]
+        if spec.feed_forward is not None:
+            subs += [("norm", spec.norm2), ("feed_forward", spec.feed_forward), ("norm", spec.norm2_out)]
+        return subs
+
+    @staticmethod
+    def tensor_needs(spec: BlockSpec) -> List[TensorNeed]:
+        out: List[TensorNeed] = []
+        subs = [("norm", spec.norm1), ("mixer", spec.mixer), ("norm", spec.norm1_out)]
+        if spec.feed_forward is not None:
+            subs += [("norm", spec.norm2), ("feed_forward", spec.feed_forward), ("norm", spec.norm2_out)]
+        for cat, sub in subs:
+            out += part_class(cat, sub.kind).tensor_needs(sub)
+        return out
+
+    def subparts(self):
+        return tuple(p for p in (self.norm1, self.mixer, self.norm1_out, self.norm2, self.feed_forward, self.norm2_out) if p is not None)
+
+    def cache_needs(self):
+        return self.mixer.cache_needs()
+
+    def load(self, tensors) -> None:
+        for p in self.subparts():
+            p.load(tensors)
+        m = float(self.spec.residual_mult)
+        self.mult = None if m == 1.0 else torch.full((self.spec.norm1.dim,), m, dtype=torch.float32, device=self.env.device)
+
+    def first_norm(self):
+        return self.norm1
+
+    def forward(self, res: Residual, ctx, cache: LayerCache) -> Residual:
+        ops, n = self.env.ops, ctx.n_tokens
+        ctx.residual = ctx.next_norm = None  # the parts' last products return their sums; the norms on them add into the stream
+        x = self.norm1.forward(res, ctx)     # adds what an earlier block left pending
+        a = self.mixer.forward(x, ctx, cache)
+        ops.norm_add(res.h, a, None, self.norm1_out.prescale_weight(), self.mult, self.norm1_out.spec.eps, n_rows=n)
+        res.sumsq = res.prescaled = res.prescaled_weight = res.operand = None
+        if self.feed_forward is not None:
+            x = self.norm2.forward(res, ctx)
+            b = self.feed_forward.forward(x, ctx)
+            ops.norm_add(res.h, b, None, self.norm2_out.prescale_weight(), self.mult, self.norm2_out.spec.eps, n_rows=n)
+        return res
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "sandwich", SandwichBlock)
 register_part("block", "post_norm", PostNormBlock)
 register_part("block", "parallel", ParallelBlock)

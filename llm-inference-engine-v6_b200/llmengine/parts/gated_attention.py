@@ -7,7 +7,7 @@ With h the mixer's input, per token at position p:
     v <- (1 - m) v + m v_first                                  (value mixing; the mixed v is what the cache holds)
     score_a(i, j) = (q_a(i) . k_b(j)) * scale,  b = a // (H / G),  j <= i in the same chunk (and inside the window)
     p_a(i, j) = exp(score) / (sum_j exp(score) + exp(sink_a))   the sink only enlarges the denominator
-    out = Wo ((heads' results side by side) * sigmoid(g))
+    out = Wo ((heads' results side by side) * sigmoid(g))       g: a gate a number of the result, or (gate_per_head) one a head
 Norms, rotation, scores, softmax and the gate are float32 in both engine precisions. v_first are the values that the
 first layer with value mixing computed for the same tokens in the same step: that layer leaves them in the step
 context (`ctx.shared`), the later ones read them there.
@@ -53,7 +53,7 @@ class GatedAttention(Mixer):
         out = [TensorNeed(spec.q_weight, (H * dk, spec.hidden)), TensorNeed(spec.k_weight, (G * dk, spec.hidden)),
                TensorNeed(spec.v_weight, (G * dv, spec.hidden)), TensorNeed(spec.o_weight, (spec.hidden, H * dv))]
         if spec.gate_weight:
-            out.append(TensorNeed(spec.gate_weight, (H * dv, spec.hidden)))
+            out.append(TensorNeed(spec.gate_weight, (H if spec.gate_per_head else H * dv, spec.hidden)))
         for name in (spec.q_norm, spec.k_norm):
             if name:
                 out.append(TensorNeed(name, (dk,), "float32", init="around_one"))
@@ -118,7 +118,7 @@ class GatedAttention(Mixer):
         att = ctx.ws.get("gated_attention.out", (n, H * dv), dt)
         g_off = H * dk + G * dk + G * dv
         ops.gated_attention(q, cache.k, cache.v, ctx, ctx.block_tables[cache.group], att, H, G, dk, dv, s.scale, s.window, s.chunk,
-                            self.sink, parts if s.gate_weight else None, g_off)
+                            self.sink, parts if s.gate_weight else None, g_off, **({"gate_per_head": True} if s.gate_per_head else {}))
         return add_into_stream_or_partials(ops, att, self.w_o, ctx, False, "gated_attention.delta")
 
 

@@ -18,8 +18,12 @@ from .spec import GatedMLPSpec, TensorNeed
 class GatedMLP(FeedForward):
     def __init__(self, spec: GatedMLPSpec, env):
         super().__init__(spec, env)
-        if spec.activation not in ("silu", "gelu_tanh"):
-            raise ValueError(f"gated feed-forward: activation '{spec.activation}' is not implemented (silu and gelu_tanh are)")
+        if spec.activation not in ("silu", "gelu_tanh", "clamped_swish"):
+            raise ValueError(f"gated feed-forward: activation '{spec.activation}' is not implemented (silu, gelu_tanh and clamped_swish are)")
+        if spec.activation == "clamped_swish" and not spec.limit > 0:
+            raise ValueError("gated feed-forward: clamped_swish needs a positive limit")
+        # what the kernels are told: a name, or for an activation with constants (name, limit, slope)
+        self.act = (spec.activation, float(spec.limit), float(spec.slope)) if spec.activation == "clamped_swish" else spec.activation
         self.w_gate_up = None
         self.w_down = None
 
@@ -85,7 +89,7 @@ class GatedMLP(FeedForward):
             else:
                 x = x.dense(ctx)
         if s.activation != "silu":
-            extra["act"] = s.activation
+            extra["act"] = self.act
         if self.blocked:
             ops.gemm_swiglu(x[:n], self.w_gate_up, act, ctx.ws, **extra)
         elif n <= 64:  # few tokens: the products may come as partial sums, added by their consumers
@@ -93,7 +97,7 @@ class GatedMLP(FeedForward):
         else:
             gate_up = ctx.ws.get("mlp.gate_up", (n, 2 * s.intermediate), self.env.dtype)
             ops.gemm(x[:n], self.w_gate_up, gate_up)
-            ops.silu_mul(gate_up, act, **({"act": s.activation} if s.activation != "silu" else {}))
+            ops.silu_mul(gate_up, act, **({"act": self.act} if s.activation != "silu" else {}))
         return add_into_stream_or_partials(ops, act, self.w_down, ctx, False, "mlp.delta")
 
 

@@ -52,4 +52,17 @@ class RMSNorm(Norm):
         return out
 
 
+class UnitOffsetRMSNorm(RMSNorm):
+    """The same norm with its weight stored around zero: y = x / sqrt(mean(x^2) + eps) * (1 + w). The sum 1 + w is formed once,
+    in float32, when the weights are loaded; the kernels are RMSNorm's."""
+
+    @staticmethod
+    def tensor_needs(spec: NormSpec) -> List[TensorNeed]:
+        return [TensorNeed(spec.weight, (spec.dim,), "float32", init="normal")]
+
+    def load(self, tensors) -> None:
+        self.weight = (tensors[self.spec.weight] + 1.0).contiguous()
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "rmsnorm_unit_offset", UnitOffsetRMSNorm)

@@ -76,7 +76,8 @@ class GroupRoutedMLP(FeedForward):
     """Gated experts chosen by scores over all experts, with a correction that only the choice sees and a limit on groups
     of experts (GroupRoutedMLPSpec), plus an optional expert that every token goes through:
 
-        s = softmax(Wr x)  (float32);  choice = s + correction;  only the best `keep_groups` of `groups` groups stay
+        s = softmax(Wr x) or sigmoid(Wr x)  (float32);  choice = s + correction;  only the best `keep_groups` of `groups` groups stay
+        (by their largest choice score, or by the sum of their two largest)
         chosen = the `top` largest choice scores;  g_e = s_e / (sum of the chosen s + norm_eps)
         out = sum_e g_e * Wdown_e (silu(Wgate_e x) * Wup_e x)  +  shared(x)
 
@@ -93,6 +94,8 @@ class GroupRoutedMLP(FeedForward):
             raise ValueError(f"routed feed-forward: cannot choose {spec.top} of {spec.experts} experts")
         if spec.groups < 1 or spec.experts % spec.groups or not (1 <= spec.keep_groups <= spec.groups):
             raise ValueError(f"routed feed-forward: {spec.experts} experts do not form {spec.groups} equal groups of which {spec.keep_groups} stay")
+        if spec.score not in ("softmax", "sigmoid") or spec.group_top not in (1, 2):
+            raise ValueError("routed feed-forward: score is 'softmax' or 'sigmoid', a group's score sums its 1 or 2 largest")
         if spec.keep_groups * (spec.experts // spec.groups) < spec.top:
             raise ValueError("routed feed-forward: the groups that stay hold fewer experts than a token uses")
         if not (len(spec.gate_weights) == len(spec.up_weights) == len(spec.down_weights) == spec.experts):
@@ -139,7 +142,11 @@ class GroupRoutedMLP(FeedForward):
         x = x[:n]
         idx = ctx.ws.get("routed.idx", (n, s.top), torch.int32)
         share = ctx.ws.get("routed.share", (n, s.top), torch.float32)
-        ops.route_grouped(x, self.router, self.correction, s.top, s.groups, s.keep_groups, s.norm_eps, idx, share)
+        if (s.score, s.group_top, s.normalize) == ("softmax", 1, True):
+            ops.route_grouped(x, self.router, self.correction, s.top, s.groups, s.keep_groups, s.norm_eps, idx, share)
+        else:
+            ops.route_grouped(x, self.router, self.correction, s.top, s.groups, s.keep_groups, s.norm_eps, idx, share,
+                              score=s.score, group_top=s.group_top, normalize=s.normalize)
         tile = ops.routed_tile_rows(n, dt, (s.hidden, s.intermediate), n * s.top / s.experts)
         tile_expert, tile_rows = ops.routed_group(idx, s.experts, tile, ctx.ws, "routed")
         act = ctx.ws.get("routed.act", (n * s.top, s.intermediate), dt)

@@ -30,6 +30,8 @@ class TensorNeed:
 
 @dataclass(frozen=True)
 class NormSpec:
+    """kind "rmsnorm": x / sqrt(mean(x^2) + eps) * weight. kind "rmsnorm_unit_offset": the same with the weight stored around
+    zero and applied as (1 + weight)."""
     kind: str
     dim: int
     eps: float
@@ -144,6 +146,7 @@ class GatedAttentionSpec:
     value_mix_weight: Optional[str] = None
     chunk: int = 0
     window: int = 0
+    gate_per_head: bool = False            # the gate is one number a head (gate_weight [heads, hidden]) instead of one a result number
 
 
 @dataclass(frozen=True)
@@ -170,15 +173,116 @@ class SelectiveScanSpec:
 
 
 @dataclass(frozen=True)
+class DecayedLinearAttentionSpec:
+    """A recurrent mixer with a matrix of state per head and a decay per key channel (kind "decayed_linear_attention",
+    parts/linear_state.py): q = Wq h * dim^(-1/2), k = Wk h (heads x dim), v = Wv h (heads x vdim);
+    a = sigmoid(W_a2 (W_a1 h) + a_bias)^(1 / tau) per head and key channel; S <- diag(a) S + k v^T; o = S^T q; every head's o is
+    divided by its root mean square (eps) and multiplied by norm_weight [vdim]; out = Wo (o * silu(Wg h))."""
+    kind: str
+    hidden: int
+    heads: int
+    dim: int
+    vdim: int
+    rank: int
+    tau: float
+    eps: float
+    q_weight: str
+    k_weight: str
+    v_weight: str
+    g_weight: str
+    o_weight: str
+    norm_weight: str
+    a1_weight: str
+    a2_weight: str
+    a2_bias: str
+
+
+@dataclass(frozen=True)
+class TokenShiftMixSpec:
+    """A recurrent mixer whose projections read blends of a token's input with the previous token's (kind "token_shift_mix",
+    parts/linear_state.py): x_s = h + (h_prev - h) * mu_s for s in r, k, v, g, w; r, k, v = W x (heads x dim); gate =
+    silu(Wg x_g); decay = exp(-exp(W_w2 tanh(W_w1 x_w) + w0)) per head and key channel; o = (S + diag(bonus) k v^T)^T r, then
+    S <- diag(decay) S + k v^T; every head's o is divided by its root mean square (eps); out = Wo (o * norm_weight * gate)."""
+    kind: str
+    hidden: int
+    heads: int
+    dim: int
+    rank: int
+    eps: float
+    mu: Tuple[str, ...]  # the blends' weights, in the order r, k, v, g, w
+    r_weight: str
+    k_weight: str
+    v_weight: str
+    g_weight: str
+    o_weight: str
+    w1_weight: str
+    w2_weight: str
+    w0: str
+    bonus: str
+    norm_weight: str
+
+
+@dataclass(frozen=True)
+class GatedDeltaSpec:
+    """The gated delta rule behind short convolutions (kind "gated_delta", parts/linear_state.py): q, k = W h (kv_heads x dim),
+    v = W h (heads x vdim), each through a causal convolution of `taps` inputs a channel (no bias) and silu; q and k made unit
+    vectors per head (x / sqrt(sum x^2 + unit_eps)), q times dim^(-1/2); beta = sigmoid(Wb h), g = exp(-exp(a_log) *
+    softplus(Wa h + dt_bias)) per head; S <- g S; w = beta (v - S^T k); S <- S + k w^T; o = S^T q; every head's o is divided by
+    its root mean square (eps) and multiplied by norm_weight [vdim]; out = Wo (o * silu(Wg h))."""
+    kind: str
+    hidden: int
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    taps: int
+    eps: float
+    q_weight: str
+    k_weight: str
+    v_weight: str
+    q_conv: str
+    k_conv: str
+    v_conv: str
+    b_weight: str
+    a_weight: str
+    a_log: str
+    dt_bias: str
+    g_weight: str
+    norm_weight: str
+    o_weight: str
+    unit_eps: float = 1e-6
+
+
+@dataclass(frozen=True)
+class MixerPairSpec:
+    """Two mixers side by side that read the same input (kind "mixer_pair", parts/mixer_pair.py). combine "weighted":
+    left_scale * left + right_scale * right. combine "normed_mean": (rms(left) * left_norm + rms(right) * right_norm) / 2, the
+    root mean square over the model width (eps inside the root), the weights [hidden] as stored."""
+    kind: str
+    hidden: int
+    left: object
+    right: object
+    combine: str = "weighted"
+    left_scale: float = 1.0
+    right_scale: float = 1.0
+    left_norm: Optional[str] = None
+    right_norm: Optional[str] = None
+    eps: float = 0.0
+
+
+@dataclass(frozen=True)
 class GatedMLPSpec:
-    """down( act(gate(x)) * up(x) ), dense, no bias. activation "silu"."""
+    """down( act(gate(x)) * up(x) ), dense, no bias. activation "silu" or "gelu_tanh"; "clamped_swish": g = min(gate(x), limit),
+    u = clamp(up(x), -limit, limit), down(g * sigmoid(slope * g) * (u + 1))."""
     kind: str
     hidden: int
     intermediate: int
     gate_weight: str
     up_weight: str
     down_weight: str
-    activation: str = "silu"  # or "gelu_tanh"
+    activation: str = "silu"
+    limit: float = 0.0
+    slope: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -200,10 +304,11 @@ class RoutedMLPSpec:
 
 @dataclass(frozen=True)
 class GroupRoutedMLPSpec:
-    """Mixture of gated experts with scores over all experts (kind "group_routed_mlp"): s = softmax(router x) in float32;
-    choice scores = s + correction (optional tensor [experts]); the experts form `groups` equal groups of neighbours, a group's
-    score is its largest choice score, and only experts of the best `keep_groups` groups can be chosen; the `top` largest
-    choice scores win; their weights are s (without the correction) divided by (their sum + norm_eps); an expert is
+    """Mixture of gated experts with scores over all experts (kind "group_routed_mlp"): s = softmax(router x) in float32, or
+    (score "sigmoid") the sigmoid of every logit; choice scores = s + correction (optional tensor [experts]); the experts form
+    `groups` equal groups of neighbours, a group's score is its largest choice score (group_top 1) or the sum of its two largest
+    (group_top 2), and only experts of the best `keep_groups` groups can be chosen; the `top` largest choice scores win; their
+    weights are s (without the correction) divided by (their sum + norm_eps), or s as it is (normalize False); an expert is
     down_e(act(gate_e x) * up_e x) without biases; `shared` (a GatedMLPSpec or None) runs for every token and is added."""
     kind: str
     hidden: int
@@ -220,6 +325,9 @@ class GroupRoutedMLPSpec:
     norm_eps: float = 1e-20
     activation: str = "silu"
     shared: object = None
+    score: str = "softmax"
+    group_top: int = 1
+    normalize: bool = True
 
 
 @dataclass(frozen=True)
@@ -247,6 +355,8 @@ class BlockSpec:
     kind "post_norm": the norms sit on the sub-layers' outputs and the sub-layers read h itself:
     h += scale1 * norm1(mixer(h)); h += scale2 * norm2(feed_forward(h)) (feed_forward and norm2 may be None); scale1 / scale2 name
     optional per-column layer-scale tensors [hidden].
+    kind "sandwich": a norm before and one after each sub-layer: h += residual_mult * norm1_out(mixer(norm1(h)));
+    h += residual_mult * norm2_out(feed_forward(norm2(h))) (feed_forward, norm2 and norm2_out may be None).
     mixer / feed_forward / token_input are any registered spec objects with a `kind`."""
     kind: str
     norm1: object
@@ -256,6 +366,9 @@ class BlockSpec:
     token_input: object = None
     scale1: Optional[str] = None
     scale2: Optional[str] = None
+    norm1_out: object = None
+    norm2_out: object = None
+    residual_mult: float = 1.0
 
 
 @dataclass(frozen=True)

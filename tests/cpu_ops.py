@@ -46,6 +46,14 @@ class CpuOps:
         return h
 
     @staticmethod
+    def _glu(g, u, act):
+        if isinstance(act, tuple):  # ("clamped_swish", limit, slope)
+            _, lim, slope = act
+            g, u = torch.clamp(g, max=lim), torch.clamp(u, -lim, lim)
+            return g * torch.sigmoid(slope * g) * (u + 1.0)
+        return CpuOps._act(g, act) * u
+
+    @staticmethod
     def _act(g, act):
         if act == "gelu_tanh":
             return 0.5 * g * (1.0 + torch.tanh(0.7978845608028654 * (g + 0.044715 * g ** 3)))
@@ -59,7 +67,7 @@ class CpuOps:
         else:
             g = gate_up[:, :ff].float()
             u = gate_up[:, ff:].float()
-        out.copy_((self._act(g, act) * u).to(out.dtype))
+        out.copy_(self._glu(g, u, act).to(out.dtype))
         return out
 
     def gemm(self, a, w, out, ws=None):
@@ -174,13 +182,14 @@ class CpuOps:
         idx.copy_(order.to(torch.int32))
         share.copy_(torch.softmax(torch.gather(z, 1, order), dim=-1))
 
-    def route_grouped(self, x, w, correction, top, groups, keep, norm_eps, idx, share):
-        s = torch.softmax(x.float() @ w.float().t(), dim=-1)
+    def route_grouped(self, x, w, correction, top, groups, keep, norm_eps, idx, share, score="softmax", group_top=1, normalize=True):
+        z = x.float() @ w.float().t()
+        s = torch.sigmoid(z) if score == "sigmoid" else torch.softmax(z, dim=-1)
         choice = s + correction if correction is not None else s.clone()
         E = s.shape[1]
         per = E // groups
         if keep < groups:
-            best = choice.view(-1, groups, per).max(-1).values
+            best = torch.sort(choice.view(-1, groups, per), dim=-1, descending=True).values[..., :min(group_top, per)].sum(-1)
             kept = torch.argsort(best, dim=-1, descending=True, stable=True)[:, :keep]
             mask = torch.zeros(s.shape[0], groups, dtype=torch.bool)
             mask.scatter_(1, kept, True)
@@ -188,7 +197,7 @@ class CpuOps:
         order = torch.argsort(choice, dim=-1, descending=True, stable=True)[:, :top]
         picked = torch.gather(s, 1, order)
         idx.copy_(order.to(torch.int32))
-        share.copy_(picked / (picked.sum(-1, keepdim=True) + norm_eps))
+        share.copy_(picked / (picked.sum(-1, keepdim=True) + norm_eps) if normalize else picked)
 
     def routed_tile_rows(self, n_tokens=0, dtype=None, inner=(), per_expert=0.0):
         return 4
@@ -296,7 +305,7 @@ class CpuOps:
                 vcache[page, :, pos % ps, :] = v.view(kv_heads, dv).to(vcache.dtype)
 
     def gated_attention(self, q, kcache, vcache, batch, block_table, out, nq, nkv, dk, dv, scale, window=0, chunk=0, sink=None,
-                        gate=None, gate_off=0):
+                        gate=None, gate_off=0, gate_per_head=False):
         ps, g = kcache.shape[2], nq // nkv
         gates = gate.sum(0) if gate is not None else None
         for t in range(batch.n_tokens):
@@ -317,7 +326,9 @@ class CpuOps:
                 else:
                     p = torch.softmax(s, dim=0)
                 o = p @ V[:, h // g, :]
-                if gates is not None:
+                if gates is not None and gate_per_head:
+                    o = o * torch.sigmoid(gates[t, gate_off + h])
+                elif gates is not None:
                     o = o * torch.sigmoid(gates[t, gate_off + h * dv:gate_off + (h + 1) * dv])
                 out[t, h * dv:(h + 1) * dv] = o.to(out.dtype)
         return out
@@ -355,6 +366,98 @@ class CpuOps:
                 y = S @ proj[t, c_off:c_off + N] + (skip * x if skip is not None else 0)
                 out[t] = (y * torch.nn.functional.silu(z[t])).to(out.dtype)
             state[slot] = S
+        return out
+
+    # ------------------------------------------------------------------ mixers with a matrix of state per head
+    def lowrank_map(self, proj, rank, weight_t, bias, out, n_tokens, in_act=None, out_act="softplus", param=0.0):
+        low = proj[:n_tokens, :rank]
+        z = (torch.tanh(low) if in_act == "tanh" else low) @ weight_t.float()
+        if bias is not None:
+            z = z + bias
+        if out_act == "sigmoid_root":
+            out[:n_tokens] = torch.sigmoid(z) ** (1.0 / param)
+        elif out_act == "exp_neg_exp":
+            out[:n_tokens] = torch.exp(-torch.exp(z))
+        else:
+            out[:n_tokens] = torch.nn.functional.softplus(z)
+        return out
+
+    def pair_combine(self, a, b, wa, wb, ca, cb, eps, out, n_rows=None):
+        n = out.shape[0] if n_rows is None else n_rows
+        ys = []
+        for t, w in ((a, wa), (b, wb)):
+            y = (t if t.dim() == 2 else t.sum(0))[:n]
+            if w is not None:
+                y = y / torch.sqrt((y * y).mean(-1, keepdim=True) + eps) * w
+            ys.append(y)
+        out[:n] = ca * ys[0] + cb * ys[1]
+        return out
+
+    def linear_state_shape(self, heads, dk, dv):
+        return (heads, dk, dv)
+
+    @staticmethod
+    def _cols(t, off, width):
+        return (t if t.dim() == 2 else t.sum(0))[:, off:off + width]
+
+    def linear_state(self, rule, q, q_off, k, k_off, v, v_off, decay, decay_off, bonus, state, batch, out, heads, kv_heads, dk, dv,
+                     q_scale=1.0, unit_eps=-1.0):
+        Q = self._cols(q, q_off, kv_heads * dk).reshape(-1, kv_heads, dk) * q_scale
+        K = self._cols(k, k_off, kv_heads * dk).reshape(-1, kv_heads, dk)
+        V = self._cols(v, v_off, heads * dv).reshape(-1, heads, dv)
+        if rule == "delta" and unit_eps >= 0:
+            Q = Q / torch.sqrt((Q / q_scale).pow(2).sum(-1, keepdim=True) + unit_eps)
+            K = K / torch.sqrt(K.pow(2).sum(-1, keepdim=True) + unit_eps)
+        rep = heads // kv_heads
+        for s in range(batch.n_seqs):
+            first, n, slot = int(batch.seq_qoff[s]), int(batch.seq_ntok[s]), int(batch.seq_slot[s])
+            S = state[slot].clone()
+            for t in range(first, first + n):
+                qt, kt, vt = Q[t].repeat_interleave(rep, 0), K[t].repeat_interleave(rep, 0), V[t]
+                kv = kt[:, :, None] * vt[:, None, :]
+                if rule == "delta":
+                    g, beta = decay[t, decay_off:decay_off + heads], decay[t, decay_off + heads:decay_off + 2 * heads]
+                    S = S * g[:, None, None]
+                    w = beta[:, None] * (vt - torch.einsum("hkv,hk->hv", S, kt))
+                    S = S + kt[:, :, None] * w[:, None, :]
+                    o = torch.einsum("hkv,hk->hv", S, qt)
+                else:
+                    a = decay[t, decay_off:decay_off + heads * dk].view(heads, dk)
+                    if rule == "decay_write_read":
+                        S = a[:, :, None] * S + kv
+                        o = torch.einsum("hkv,hk->hv", S, qt)
+                    else:
+                        o = torch.einsum("hkv,hk->hv", S + bonus.view(heads, dk)[:, :, None] * kv, qt)
+                        S = a[:, :, None] * S + kv
+                out[t] = o.reshape(-1)
+            state[slot] = S
+        return out
+
+    def token_shift(self, x, mu, shift_state, batch, out):
+        for s in range(batch.n_seqs):
+            first, n, slot = int(batch.seq_qoff[s]), int(batch.seq_ntok[s]), int(batch.seq_slot[s])
+            if n <= 0:
+                continue
+            cur = x[first:first + n].float()
+            prev = torch.cat([shift_state[slot][None, :], cur[:-1]], dim=0)
+            out[:, first:first + n] = (cur[None] + (prev - cur)[None] * mu[:, None, :]).to(out.dtype)
+            shift_state[slot] = cur[-1]
+        return out
+
+    def delta_gates(self, a, a_off, b, b_off, a_log, dt_bias, out, n_tokens):
+        H = a_log.numel()
+        za = self._cols(a, a_off, H)[:n_tokens] + dt_bias
+        out[:n_tokens, :H] = torch.exp(-torch.exp(a_log) * torch.nn.functional.softplus(za))
+        out[:n_tokens, H:] = torch.sigmoid(self._cols(b, b_off, H)[:n_tokens])
+        return out
+
+    def head_norm_gate(self, o, weight, gate, gate_off, eps, out, n_tokens, heads, dv):
+        y = o[:n_tokens].view(n_tokens, heads, dv)
+        y = y / torch.sqrt((y * y).mean(-1, keepdim=True) + eps) * (weight.view(heads, dv) if weight.numel() == heads * dv and heads > 1 else weight)
+        y = y.reshape(n_tokens, heads * dv)
+        if gate is not None:
+            y = y * torch.nn.functional.silu(self._cols(gate, gate_off, heads * dv)[:n_tokens])
+        out[:n_tokens] = y.to(out.dtype)
         return out
 
     def decode_attention_fusable(self, batch, kcache, nq, nkv, hd, out):
