@@ -321,7 +321,7 @@ def run_workload(args):
     """The serving workloads that go with the larger geometries: `serve` = 32 requests with prompts of
     16 to 2,048 random tokens and 256 new tokens each through the continuous-batching scheduler;
     `long` = one prompt of 16,384 tokens in portions of 2,048, then 512 decoded tokens. Prints one JSON
-    line of its own (not the contract's line): tokens a second over the whole run, and `host_wait_share`: the part of the wall
+    line of its own (not the default line): tokens a second over the whole run, and `host_wait_share`: the part of the wall
     time that the host spent blocked, waiting for the device to finish a step. While it waits the host
     is no bound; the rest (`host_busy_share`: planning, batch building, launching the kernels of prompt
     and mixed steps one by one, most of it beside a busy device) is the most that the host can cost."""
@@ -480,7 +480,33 @@ ZULOPEL_SIZES = {
     "w1024": (zulopel_sizes(1024, 16, 4, 64, 64, 1024, 2048, 16, 64, 8, 2, 4, 2, 1408, 1408, 4, 32768), DESIGN_SIZES["w1024"][0]),
     "w2048": (zulopel_sizes(2048, 32, 8, 64, 64, 1024, 4096, 16, 128, 16, 4, 4, 2, 2048, 2048, 4, 32768), DESIGN_SIZES["w2048"][0]),
 }
-DESIGNS = {"vapelix": DESIGN_SIZES, "zulopel": ZULOPEL_SIZES}
+
+
+def selinex_sizes(width, heads, kv_heads, dim, window, state_heads, state_dim, ff, experts, top, groups, keep, expert_ff, layers, vocab):
+    def att(rot):
+        m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "mask": {"size": window}}
+        if rot:
+            m["rot"] = {"dims": dim, "base": 500000.0}
+        return m
+    pair = {"left": att(False), "right": {"heads": state_heads, "dim": state_dim // 2, "vdim": state_dim, "tau": 16.0, "rank": 16},
+            "left_scale": 1.0, "right_scale": 1.0}
+    pair2 = {"left": att(True), "right": {"heads": width // 64, "dim": 64, "rank": 64}}
+    delta = {"heads": state_heads, "kv_heads": state_heads, "dim": state_dim, "vdim": state_dim, "conv": 4}
+    dense = {"kind": "dense", "ff": ff, "limit": 7.0}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top, "groups": {"count": groups, "keep": keep}}}
+    kinds = [("parallel", pair, moe), ("delta", delta, dense), ("parallel_2", pair2, moe), ("delta", delta, moe)]
+    return {"architecture": "Selinex", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.7, "max_positions": 8192,
+            "layers": [{"type": t, "mixer": m, "mlp": f} for t, m, f in (kinds[i % 4] for i in range(layers))]}
+
+
+# Selinex: windowed attention beside a linear-state mixer (a decay a key channel, or token shift) in turn with gated-delta layers,
+# routed experts chosen by sigmoid scores within groups and clamped dense feed-forwards; beside it the Zulopel configuration of the
+# same name (recurrent and attention layers in turn, routed experts within groups: the closest existing model)
+SELINEX_SIZES = {
+    "w1024": (selinex_sizes(1024, 16, 4, 64, 1024, 8, 128, 2816, 8, 2, 4, 2, 1408, 4, 32768), ZULOPEL_SIZES["w1024"][0]),
+    "w2048": (selinex_sizes(2048, 32, 8, 64, 1024, 16, 128, 8192, 16, 4, 4, 2, 2048, 4, 32768), ZULOPEL_SIZES["w2048"][0]),
+}
+DESIGNS = {"vapelix": DESIGN_SIZES, "zulopel": ZULOPEL_SIZES, "selinex": SELINEX_SIZES}
 
 
 def run_design(args):
@@ -586,7 +612,7 @@ def main():
     ap.add_argument("--skip", default="", help="comma list of parts to leave out: decode,e2e,prefill,points (for profiling runs)")
     ap.add_argument("--no-cuda-graphs", dest="graphs", action="store_false", help="launch decode steps kernel by kernel")
     ap.add_argument("--workload", choices=["decode", "serve", "long"], default="decode",
-                    help="decode: the contract's line (default). serve / long: the workloads of the 3B and 8B configurations, a line of their own")
+                    help="decode: the default line. serve / long: the workloads of the 3B and 8B configurations, a line of their own")
     ap.add_argument("--budget", type=int, default=2048, help="serve: prompt tokens a step (max_prefill_tokens_per_step)")
     ap.add_argument("--design", choices=sorted(DESIGNS), default=None,
                     help="instead of the default line: prompt and decode throughput of this design at a few layer sizes, "

@@ -50,6 +50,9 @@ class Model:
                 self.portion_multiple = math.lcm(self.portion_multiple, m)
         self.caches: List[LayerCache] = [LayerCache() for _ in range(n_runs)]
         self.weight_bytes = 0
+        # for looking at a model layer by layer: called as after_run(run index, float32 stream [tokens, hidden]) behind every
+        # run of a layer, with everything that the run left pending added (the same sum the next norm would have made)
+        self.after_run = None
 
     # ------------------------------------------------------------------ weights
     def load(self, model_dir: str) -> None:
@@ -130,6 +133,11 @@ class Model:
                 res.sumsq = res.prescaled = res.prescaled_weight = None
             ctx.norm_after_block = self.blocks[order[r + 1].layer].first_norm() if r + 1 < len(order) else self.final_norm
             res = self.blocks[run.layer].forward(res, ctx, self.caches[r])
+            if self.after_run is not None:
+                if res.pending is not None:
+                    self.env.ops.stream_add(res.h, res.pending, None, n_rows=ctx.n_tokens)
+                    res.pending = res.sumsq = res.prescaled = res.prescaled_weight = res.operand = None
+                self.after_run(r, res.h[:ctx.n_tokens])
         ctx.next_norm = ctx.norm_after_block = None
         if ctx.n_rows > 0:
             if self.final_norm.can_defer and self.head.wants_lazy_norm(ctx):

@@ -55,6 +55,15 @@ def read_model(model_dir, dtype=torch.float64):
 
 
 # ---------------------------------------------------------------------------- small pieces
+ROUNDING = None  # a function, or None. A 16-bit engine rounds the operands of its matrix products (a sublayer's input, queries, keys and
+# values, what enters an output projection or an expert's last matrix); with ROUNDING set, the same happens here, everything else
+# staying in the precision of the weights: the difference to a run without it is the error that rounding alone causes.
+
+
+def _r(x):
+    return x if ROUNDING is None else ROUNDING(x)
+
+
 def rms(x, eps):
     return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
 
@@ -106,6 +115,7 @@ def window_attention(h, w, p, m, st, gated):
         v = (w[p + "v"] @ h[t]).view(G, dv)
         if rot:
             q, k = rotate(q, pos, rot["dims"], rot["base"]), rotate(k, pos, rot["dims"], rot["base"])
+        q, k, v = _r(q), _r(k), _r(v)
         st.setdefault("k", []).append(k)
         st.setdefault("v", []).append(v)
         lo = max(0, pos - size + 1) if size else 0
@@ -119,7 +129,7 @@ def window_attention(h, w, p, m, st, gated):
                 o = o * gate[a]
             out[t, a * dv:(a + 1) * dv] = o
     st["n"] = pos0 + T
-    return out @ w[p + "o"].t()
+    return _r(out) @ w[p + "o"].t()
 
 
 # ---------------------------------------------------------------------------- recurrence with a decay per key channel
@@ -142,7 +152,7 @@ def decayed_linear_attention(h, w, p, m, st, eps):
         o = rms(o, eps) * w[p + "norm"]
         out[t] = o.reshape(-1) * silu(w[p + "g"] @ h[t])
     st["S"] = S
-    return out @ w[p + "o"].t()
+    return _r(out) @ w[p + "o"].t()
 
 
 # ---------------------------------------------------------------------------- token-shift recurrence with a bonus
@@ -159,7 +169,7 @@ def token_shift_recurrence(h, w, p, m, st, eps):
     out = torch.zeros(T, H * dk, dtype=h.dtype)
     u = w[p + "u"].view(H, dk)
     for t in range(T):
-        mix = {s: h[t] + (prev - h[t]) * w[p + "mu." + s] for s in "rkvgw"}
+        mix = {s: _r(h[t] + (prev - h[t]) * w[p + "mu." + s]) for s in "rkvgw"}
         r = (w[p + "r"] @ mix["r"]).view(H, dk)
         k = (w[p + "k"] @ mix["k"]).view(H, dk)
         v = (w[p + "v"] @ mix["v"]).view(H, dk)
@@ -172,7 +182,7 @@ def token_shift_recurrence(h, w, p, m, st, eps):
         out[t] = o * gate
         prev = h[t]
     st["S"], st["prev"] = S, prev
-    return out @ w[p + "o"].t()
+    return _r(out) @ w[p + "o"].t()
 
 
 # ---------------------------------------------------------------------------- gated delta rule
@@ -217,7 +227,7 @@ def gated_delta(h, w, p, m, st, eps):
         o = rms(o, eps) * w[p + "norm"]
         out[t] = o.reshape(-1) * silu(w[p + "g"] @ h[t])
     st["S"] = S
-    return out @ w[p + "o"].t()
+    return _r(out) @ w[p + "o"].t()
 
 
 # ---------------------------------------------------------------------------- mixers of a layer
@@ -241,7 +251,7 @@ def dense_ff(h, w, p, f):
     lim = f["limit"]
     g = torch.clamp(h @ w[p + "gate"].t(), max=lim)
     u = torch.clamp(h @ w[p + "up"].t(), -lim, lim)
-    return (g * sigmoid(1.702 * g) * (u + 1.0)) @ w[p + "down"].t()
+    return _r(g * sigmoid(1.702 * g) * (u + 1.0)) @ w[p + "down"].t()
 
 
 def choose_experts(z, correction, top, groups, keep):
@@ -269,7 +279,7 @@ def routed_ff(h, w, p, f):
         chosen, share = choose_experts(w[p + "router"] @ h[t], w[p + "correction"], r["top"], gr.get("count", 0), gr.get("keep", 0))
         for e, g in zip(chosen.tolist(), share):
             q = f"{p}e{e}."
-            out[t] += g * (w[q + "down"] @ (silu(w[q + "gate"] @ h[t]) * (w[q + "up"] @ h[t])))
+            out[t] += g * (w[q + "down"] @ _r(silu(w[q + "gate"] @ h[t]) * (w[q + "up"] @ h[t])))
     return out
 
 
@@ -298,16 +308,16 @@ def forward(cfg, w, tokens, seq=None, after_layers=None):
     x = w["embed"][torch.as_tensor(tokens, dtype=torch.long)]
     for r, i in enumerate(layer_order(cfg)):
         l, p = cfg["layers"][i], f"l{i}."
-        y = mixer(l["type"], norm_one_plus(x, w[p + "norm1"], eps), w, p + "mix.", l["mixer"], seq.runs[r], eps)
+        y = mixer(l["type"], _r(norm_one_plus(x, w[p + "norm1"], eps)), w, p + "mix.", l["mixer"], seq.runs[r], eps)
         x = x + m * norm_one_plus(y, w[p + "norm1b"], eps)
         f = l.get("mlp")
         if f:
-            hh = norm_one_plus(x, w[p + "norm2"], eps)
+            hh = _r(norm_one_plus(x, w[p + "norm2"], eps))
             y = dense_ff(hh, w, p + "mlp.", f) if f["kind"] == "dense" else routed_ff(hh, w, p + "mlp.", f)
             x = x + m * norm_one_plus(y, w[p + "norm2b"], eps)
         if after_layers is not None:
             after_layers.append(x.clone())
-    return norm_one_plus(x, w["final.norm"], eps) @ w["embed"].t()
+    return _r(norm_one_plus(x, w["final.norm"], eps)) @ w["embed"].t()
 
 
 def greedy(cfg, w, prompt, n_new):

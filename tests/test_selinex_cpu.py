@@ -255,6 +255,23 @@ def test_engine_on_the_test_double_matches_plain(cpu_engine):
     assert eng.cm.num_requests == 0
 
 
+def test_stream_after_every_layer_run_on_the_test_double(cpu_engine):
+    """Model.after_run sees the stream behind every run of a layer; a looped layer counts each time."""
+    eng, (pc, pw), cfg = cpu_engine
+    ids = random_ids(23, cfg["vocab"], 4)
+    want, got = [], []
+    P.forward(pc, pw, ids, after_layers=want)
+    model = eng._ensure_model()
+    model.after_run = lambda r, h: got.append((r, h.clone()))
+    try:
+        eng.run_step([(8, ids, [len(ids) - 1])], end=[8])
+    finally:
+        model.after_run = None
+    assert [r for r, _ in got] == list(range(len(P.layer_order(cfg)))) and len(want) == len(got)
+    for (r, a), b in zip(got, want):
+        assert float((a.double() - b).abs().max()) < 2e-4 * max(1.0, float(b.abs().max())), r
+
+
 def test_generation_through_the_scheduler_matches_plain(cpu_engine):
     eng, (pc, pw), cfg = cpu_engine
     prompt = random_ids(9, cfg["vocab"], 3)
