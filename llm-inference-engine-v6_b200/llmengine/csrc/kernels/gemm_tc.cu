@@ -157,6 +157,7 @@ struct EpiArgs {
   int* counters = nullptr;                             // MEET: one per tile of outputs, zero between launches
   const float* in_sumsq = nullptr; int n_in_sumsq = 0; // SCALE: [tokens, n_in_sumsq] parts of the sums of squares
   float inv_dim = 0.f, eps = 0.f;                      // SCALE: 1 / sqrt(sum * inv_dim + eps)
+  float act_p0 = 0.f, act_p1 = 1.f;                    // SWIGLU 3: the limit and the sigmoid's slope
 };
 
 // grid: (tiles of A rows, tiles of B rows, K splits); block: 128 threads.
@@ -170,6 +171,17 @@ template <int ACT>
 __device__ __forceinline__ float gate_act(float g) {
   if (ACT == 2) return 0.5f * g * (1.0f + tanhf(0.79788456080286535588f * (g + 0.044715f * g * g * g)));
   return g / (1.0f + expf(-g));
+}
+// What the epilogue writes for a gate and its up value. SWIGLU 3: both limited, a sigmoid of slope p1 on the gate, the up side
+// raised by one: g <- min(g, p0), u <- clamp(u, -p0, p0), g * sigmoid(p1 g) * (u + 1); else gate_act(g) * u.
+template <int ACT>
+__device__ __forceinline__ float gate_up(float g, float u, float p0, float p1) {
+  if (ACT == 3) {
+    g = fminf(g, p0);
+    u = fminf(fmaxf(u, -p0), p0);
+    return g / (1.0f + expf(-p1 * g)) * (u + 1.0f);
+  }
+  return gate_act<ACT>(g) * u;
 }
 
 template <int BN, bool SWAP, typename TO, int SWIGLU = false, int EPI = EPI_NONE>
@@ -304,7 +316,7 @@ __global__ void __launch_bounds__(128)
         tmem_load16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)c0, gv);
         tmem_load16(tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(c0 + BN / 2), uv);
 #pragma unroll
-        for (int i = 0; i < 16; ++i) gv[i] = gate_act<SWIGLU>(gv[i]) * uv[i];
+        for (int i = 0; i < 16; ++i) gv[i] = gate_up<SWIGLU>(gv[i], uv[i], epi.act_p0, epi.act_p1);
         const int col0 = b_row0 / 2 + c0;  // column of the activation matrix [tokens, RB / 2]
         if (ra < RA && col0 < RB / 2) {
           TO* dst = o + (size_t)ra * ldo + col0;
@@ -419,7 +431,7 @@ template <typename TO, int SWIGLU, int BN>
 __global__ void __launch_bounds__(PERSIST_THREADS)
     gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                               TO* __restrict__ out, int RA, int RB, int k_tiles, long long ldo, int stages, int m_tiles,
-                              int n_tiles, int* __restrict__ error_out, int add_into) {
+                              int n_tiles, int* __restrict__ error_out, int add_into, float act_p0, float act_p1) {
   static_assert(BN == 256 || BN == 192, "two accumulators of BN columns, 256 columns apart, in 512 columns of tensor memory");
   static_assert(!SWIGLU || BN == 256, "the gate|up blocks are 256 rows");
   constexpr int ACC_STRIDE = 256;  // tensor-memory columns from one accumulator to the other
@@ -556,7 +568,7 @@ __global__ void __launch_bounds__(PERSIST_THREADS)
           tmem_load16(acc + (uint32_t)c0, gv);
           tmem_load16(acc + (uint32_t)(c0 + BN / 2), uv);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) gv[i] = gate_act<SWIGLU>(gv[i]) * uv[i];
+          for (int i = 0; i < 16; ++i) gv[i] = gate_up<SWIGLU>(gv[i], uv[i], act_p0, act_p1);
           const int col0 = b_row0 / 2 + c0;  // column of the activation matrix [tokens, RB / 2]
           if (ra < RA && col0 < RB / 2) {
             TO* dst = out + (size_t)ra * ldo + col0;
@@ -654,7 +666,7 @@ template <typename TO, int SWIGLU>
 __global__ void __launch_bounds__(PERSIST_THREADS)
     gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, TO* __restrict__ out,
                         int RA, int RB, int k_tiles, long long ldo, int stages, int mp_tiles, int n_tiles,
-                        int* __restrict__ error_out) {
+                        int* __restrict__ error_out, float act_p0, float act_p1) {
   constexpr int BN = 256;                  // outputs per tile; each CTA holds BN / 2 weight rows of it
   constexpr int B_HALF_BYTES = (BN / 2) * BK * 2;
   constexpr int STAGE_BYTES = A_BYTES + B_HALF_BYTES;  // per CTA
@@ -790,7 +802,7 @@ __global__ void __launch_bounds__(PERSIST_THREADS)
           tmem_load16(acc + (uint32_t)c0, gv);
           tmem_load16(acc + (uint32_t)(c0 + BN / 2), uv);
 #pragma unroll
-          for (int i = 0; i < 16; ++i) gv[i] = gate_act<SWIGLU>(gv[i]) * uv[i];
+          for (int i = 0; i < 16; ++i) gv[i] = gate_up<SWIGLU>(gv[i], uv[i], act_p0, act_p1);
           const int col0 = b_row0 / 2 + c0;
           if (ra < RA && col0 < RB / 2) {
             TO* dst = out + (size_t)ra * ldo + col0;
@@ -831,7 +843,7 @@ __global__ void __launch_bounds__(PERSIST_THREADS)
 
 template <typename TO, int SWIGLU>
 int launch_tc_pair(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int RA, int RB, int K, long long ldo, int n_sms,
-                   cudaStream_t stream) {
+                   cudaStream_t stream, float act_p0 = 0.f, float act_p1 = 1.f) {
   constexpr int STAGE_BYTES = A_BYTES + 128 * BK * 2;
   const int k_tiles = (K + BK - 1) / BK;
   const int stages = 6;
@@ -848,13 +860,13 @@ int launch_tc_pair(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int 
   const int mp_tiles = (RA + 255) / 256, n_tiles = (RB + 255) / 256;
   const int pairs = std::min(mp_tiles * n_tiles, n_sms / 2);
   launch_kernel_cluster(kernel, 2 * pairs, PERSIST_THREADS, smem, dim3(2, 1, 1), stream, ma, mb, (TO*)out, RA, RB, k_tiles, ldo, stages, mp_tiles,
-                        n_tiles, error_word());
+                        n_tiles, error_word(), act_p0, act_p1);
   return LLM_OK;
 }
 
 template <typename TO, int SWIGLU, int BN = 256>
 int launch_tc_persistent(const CUtensorMap& ma, const CUtensorMap& mb, void* out, int RA, int RB, int K, long long ldo,
-                         int n_sms, cudaStream_t stream, int add_into = 0) {
+                         int n_sms, cudaStream_t stream, int add_into = 0, float act_p0 = 0.f, float act_p1 = 1.f) {
   constexpr int STAGE_BYTES = A_BYTES + BN * BK * 2;
   const int k_tiles = (K + BK - 1) / BK;
   const int stages = BN == 256 ? 4 : 5;
@@ -871,7 +883,7 @@ int launch_tc_persistent(const CUtensorMap& ma, const CUtensorMap& mb, void* out
   const int m_tiles = (RA + BM - 1) / BM, n_tiles = (RB + BN - 1) / BN;
   const int grid = std::min(m_tiles * n_tiles, n_sms);
   launch_kernel(kernel, grid, PERSIST_THREADS, smem, stream, ma, mb, (TO*)out, RA, RB, k_tiles, ldo, stages, m_tiles, n_tiles,
-                error_word(), add_into);
+                error_word(), add_into, act_p0, act_p1);
   return LLM_OK;
 }
 
@@ -1111,33 +1123,37 @@ extern "C" int llm_gemm_tc_scaled(const void* a, const void* w, float* out, int 
   return LLM_OK;
 }
 
-// act[m, c] = f(g[m, c]) * u[m, c] (f: silu for act 0, the tanh gelu for act 1) with g | u = a . w^T, for w [2*FF, K] whose rows are blocks of
-// 128 gate rows followed by the 128 matching up rows (FF a multiple of 128). act: bf16 [M, FF].
+// act[m, c] = f(g[m, c]) * u[m, c] (f: silu for act 0, the tanh gelu for act 1), or for act 2 min(g, p0) * sigmoid(p1 * min(g, p0)) *
+// (clamp(u, -p0, p0) + 1), with g | u = a . w^T, for w [2*FF, K] whose rows are blocks of 128 gate rows followed by the 128 matching
+// up rows (FF a multiple of 128). act: bf16 [M, FF].
 extern "C" int llm_gemm_tc_swiglu(const void* a, const void* w, void* out_act, int M, int FF, int K, long long lda, long long ldw,
-                                  long long ld_act, int act, cudaStream_t stream) {
+                                  long long ld_act, int act, float p0, float p1, cudaStream_t stream) {
   if (M == 0 || FF == 0) return LLM_OK;
   LLM_REQUIRE(llm_gemm_tc_supported(a, w, M, 2 * FF, K, lda, ldw), "gemm_tc_swiglu: operands must be 16-byte aligned with K and row strides multiples of 8");
-  LLM_REQUIRE(act == 0 || act == 1, "gemm_tc_swiglu: unknown activation %d (0 silu, 1 tanh gelu)", act);
+  LLM_REQUIRE(act >= 0 && act <= 2, "gemm_tc_swiglu: unknown activation %d (0 silu, 1 tanh gelu, 2 clamped swish)", act);
   LLM_REQUIRE(FF % 128 == 0, "gemm_tc_swiglu: the intermediate size %d must be a multiple of 128", FF);
   LLM_REQUIRE(error_word() != nullptr, "gemm_tc_swiglu: cannot allocate the error word");
   CUtensorMap ma, mb;
   LLM_REQUIRE(tensor_map_for(a, M, K, lda, BM, &ma) && tensor_map_for(w, 2 * FF, K, ldw, 256, &mb), "gemm_tc_swiglu: cuTensorMapEncodeTiled failed");
   const int form = llm_gemm_tc_form(M, 2 * FF, K, 1);
+  const int n_sms = sm_count();
+  int rc;
   if (form == FORM_PAIRS) {
     LLM_REQUIRE(tensor_map_for(w, 2 * FF, K, ldw, 128, &mb), "gemm_tc_swiglu: cuTensorMapEncodeTiled failed");
-    const int rc2 = act == 1 ? launch_tc_pair<bf16, 2>(ma, mb, out_act, M, 2 * FF, K, ld_act, sm_count(), stream)
-                             : launch_tc_pair<bf16, 1>(ma, mb, out_act, M, 2 * FF, K, ld_act, sm_count(), stream);
-    if (rc2 != LLM_OK) return rc2;
-    LLM_CHECK_LAUNCH("gemm_tc_swiglu");
-    return LLM_OK;
+    rc = act == 2   ? launch_tc_pair<bf16, 3>(ma, mb, out_act, M, 2 * FF, K, ld_act, n_sms, stream, p0, p1)
+         : act == 1 ? launch_tc_pair<bf16, 2>(ma, mb, out_act, M, 2 * FF, K, ld_act, n_sms, stream)
+                    : launch_tc_pair<bf16, 1>(ma, mb, out_act, M, 2 * FF, K, ld_act, n_sms, stream);
+  } else if (form == FORM_PERSISTENT_256) {
+    rc = act == 2   ? launch_tc_persistent<bf16, 3>(ma, mb, out_act, M, 2 * FF, K, ld_act, n_sms, stream, 0, p0, p1)
+         : act == 1 ? launch_tc_persistent<bf16, 2>(ma, mb, out_act, M, 2 * FF, K, ld_act, n_sms, stream)
+                    : launch_tc_persistent<bf16, 1>(ma, mb, out_act, M, 2 * FF, K, ld_act, n_sms, stream);
+  } else {
+    EpiArgs epi;
+    epi.act_p0 = p0; epi.act_p1 = p1;
+    rc = act == 2   ? launch_tc<256, false, bf16, 3>(ma, mb, out_act, M, 2 * FF, K, 1, ld_act, 0, 4, stream, epi)
+         : act == 1 ? launch_tc<256, false, bf16, 2>(ma, mb, out_act, M, 2 * FF, K, 1, ld_act, 0, 4, stream)
+                    : launch_tc<256, false, bf16, 1>(ma, mb, out_act, M, 2 * FF, K, 1, ld_act, 0, 4, stream);
   }
-  int rc;
-  if (act == 1)
-    rc = form == FORM_PERSISTENT_256 ? launch_tc_persistent<bf16, 2>(ma, mb, out_act, M, 2 * FF, K, ld_act, sm_count(), stream)
-                                     : launch_tc<256, false, bf16, 2>(ma, mb, out_act, M, 2 * FF, K, 1, ld_act, 0, 4, stream);
-  else
-    rc = form == FORM_PERSISTENT_256 ? launch_tc_persistent<bf16, 1>(ma, mb, out_act, M, 2 * FF, K, ld_act, sm_count(), stream)
-                                     : launch_tc<256, false, bf16, 1>(ma, mb, out_act, M, 2 * FF, K, 1, ld_act, 0, 4, stream);
   if (rc != LLM_OK) return rc;
   LLM_CHECK_LAUNCH("gemm_tc_swiglu");
   return LLM_OK;

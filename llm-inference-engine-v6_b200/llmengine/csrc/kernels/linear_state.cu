@@ -26,7 +26,8 @@
 namespace {
 
 constexpr int KPT = 16;       // state numbers of a column that one lane holds
-constexpr int LS_THREADS = 128;
+constexpr int LS_THREADS = 128;  // threads that hold the state
+constexpr int LS_BLOCK = 256;    // with the warps that fetch the next tile of tokens
 
 __device__ __forceinline__ float parts_sum(const float* __restrict__ p, int n_parts, size_t pstride, size_t i) {
   float s = p[i];
@@ -49,8 +50,102 @@ struct LinearStateParams {
   float q_scale, unit_eps;
 };
 
+// A tile of tokens through the rule: s the thread's numbers of its column, q_s / k_s / a_s the tile's rows in shared memory,
+// v_s[tt * v_stride + v_idx] the column's value; out points at the column's result of the tile's first token. A lane's sixteen
+// products are summed as four interleaved chains ((c0 + c1) + (c2 + c3), chain i taking m = i, i + 4, ...), which shortens the
+// dependent chain of a token fourfold; the order is fixed, so a token's result is the same in every step that computes it.
 template <int MODE>
-__global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(const LinearStateParams p) {
+__device__ __forceinline__ void walk_tile(float (&s)[KPT], const float (&u)[KPT], const float* __restrict__ q_s, const float* __restrict__ k_s,
+                                          const float* __restrict__ a_s, int a_stride, const float* __restrict__ v_s, int v_stride, int v_idx,
+                                          int cnt, int dkp, int R, int lane_r, bool live, float* __restrict__ out, size_t out_stride) {
+#pragma unroll 2
+  for (int tt = 0; tt < cnt; ++tt) {
+    const float* qt = q_s + tt * dkp + lane_r;
+    const float* kt = k_s + tt * dkp + lane_r;
+    const float vj = live ? v_s[tt * v_stride + v_idx] : 0.f;
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    if (MODE == 0) {
+      const float* at = a_s + tt * a_stride + lane_r;
+#pragma unroll
+      for (int m = 0; m < KPT; ++m) {
+        s[m] = fmaf(kt[R * m], vj, at[R * m] * s[m]);
+        acc[m & 3] = fmaf(s[m], qt[R * m], acc[m & 3]);
+      }
+    } else if (MODE == 1) {
+      const float* at = a_s + tt * a_stride + lane_r;
+#pragma unroll
+      for (int m = 0; m < KPT; ++m) {
+        const float kv = kt[R * m] * vj;
+        acc[m & 3] = fmaf(fmaf(u[m], kv, s[m]), qt[R * m], acc[m & 3]);
+        s[m] = fmaf(at[R * m], s[m], kv);
+      }
+    } else {
+      const float g = a_s[tt * a_stride], beta = a_s[tt * a_stride + 1];
+      float dot[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int m = 0; m < KPT; ++m) {
+        s[m] *= g;
+        dot[m & 3] = fmaf(s[m], kt[R * m], dot[m & 3]);
+      }
+      float d = (dot[0] + dot[1]) + (dot[2] + dot[3]);
+      for (int o = R >> 1; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+      const float w = beta * (vj - d);
+#pragma unroll
+      for (int m = 0; m < KPT; ++m) {
+        s[m] = fmaf(kt[R * m], w, s[m]);
+        acc[m & 3] = fmaf(s[m], qt[R * m], acc[m & 3]);
+      }
+    }
+    float r = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+    for (int o = R >> 1; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+    if (live && lane_r == 0) out[(size_t)tt * out_stride] = r;
+  }
+}
+
+// One token's row into a tile's shared memory, by one warp: the sums of the products' parts, the unit norms and the query's scale.
+template <int MODE>
+__device__ __forceinline__ void load_token(const LinearStateParams& p, size_t row, int head, int kvh, int dk, int dkp, int dv, int lane,
+                                           float* __restrict__ q_row, float* __restrict__ k_row, float* __restrict__ a_row,
+                                           float* __restrict__ v_row) {
+  float ssq = 0.f, ssk = 0.f;
+  for (int i = lane; i < dkp; i += 32) {
+    float qv = 0.f, kv = 0.f, av = 0.f;
+    if (i < dk) {
+      qv = parts_sum(p.q.p, p.q.n, p.q.stride, row * p.q.width + p.q.off + (size_t)kvh * dk + i);
+      kv = parts_sum(p.k.p, p.k.n, p.k.stride, row * p.k.width + p.k.off + (size_t)kvh * dk + i);
+      if (MODE != 2) av = p.decay[row * p.decay_width + p.decay_off + (size_t)head * dk + i];
+    }
+    ssq = fmaf(qv, qv, ssq);
+    ssk = fmaf(kv, kv, ssk);
+    q_row[i] = qv;
+    k_row[i] = kv;
+    if (MODE != 2) a_row[i] = av;
+  }
+  for (int j = lane; j < dv; j += 32) v_row[j] = parts_sum(p.v.p, p.v.n, p.v.stride, row * p.v.width + p.v.off + (size_t)head * dv + j);
+  float qmul = p.q_scale, kmul = 1.0f;
+  if (MODE == 2) {
+    ssq = warp_sum(ssq);
+    ssk = warp_sum(ssk);
+    if (p.unit_eps >= 0.f) {
+      qmul = p.q_scale / sqrtf(ssq + p.unit_eps);
+      kmul = 1.0f / sqrtf(ssk + p.unit_eps);
+    }
+    if (lane == 0) {
+      a_row[0] = p.decay[row * p.decay_width + p.decay_off + head];
+      a_row[1] = p.decay[row * p.decay_width + p.decay_off + p.H + head];
+    }
+  }
+  for (int i = lane; i < dkp; i += 32) {  // the lane's own numbers again
+    q_row[i] *= qmul;
+    if (MODE == 2) k_row[i] *= kmul;
+  }
+}
+
+// Threads 0 .. LS_THREADS - 1 hold the state and walk; the warps behind them only fetch: while the walkers are in tile i of
+// the request's tokens, the fetchers fill the other buffer with tile i + 1, and the block meets once a tile. (The first tile is
+// fetched by all warps; a decode step has only that one.)
+template <int MODE>
+__global__ void __launch_bounds__(LS_BLOCK) linear_state_kernel(const LinearStateParams p) {
   extern __shared__ float sh_ls[];
   dep_launch();
   dep_wait();
@@ -60,14 +155,27 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(const LinearSt
   const int first = p.seq_qoff[seq];
   const int dkp = R * KPT;
   const int kvh = head / (p.H / p.G);
+  const bool walker = threadIdx.x < LS_THREADS;
   const int lane_r = threadIdx.x & (R - 1);
   const int col = blockIdx.x * (LS_THREADS / R) + threadIdx.x / R;
-  const bool live = col < dv;
+  const bool live = walker && col < dv;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  float* q_s = sh_ls;                              // [tile][dkp]
-  float* k_s = q_s + (size_t)p.tile * dkp;         // [tile][dkp]
-  float* a_s = k_s + (size_t)p.tile * dkp;         // [tile][dkp] (MODE 0/1) or [tile][2] (MODE 2)
-  float* v_s = a_s + (size_t)p.tile * (MODE == 2 ? 2 : dkp);  // [tile][dv]
+  const int a_stride = MODE == 2 ? 2 : dkp;
+  const size_t buf_floats = (size_t)p.tile * (2 * dkp + a_stride + dv);
+  auto rows_of = [&](int buf, float*& q_s, float*& k_s, float*& a_s, float*& v_s) {
+    q_s = sh_ls + (size_t)buf * buf_floats;  // [tile][dkp]
+    k_s = q_s + (size_t)p.tile * dkp;        // [tile][dkp]
+    a_s = k_s + (size_t)p.tile * dkp;        // [tile][dkp] (MODE 0/1) or [tile][2] (MODE 2)
+    v_s = a_s + (size_t)p.tile * a_stride;   // [tile][dv]
+  };
+  auto fetch = [&](int t0, int buf, int w, int n_w) {
+    float *q_s, *k_s, *a_s, *v_s;
+    rows_of(buf, q_s, k_s, a_s, v_s);
+    const int cnt = min(p.tile, n_tok - t0);
+    for (int tt = w; tt < cnt; tt += n_w)
+      load_token<MODE>(p, (size_t)(first + t0 + tt), head, kvh, dk, dkp, dv, lane, q_s + tt * dkp, k_s + tt * dkp, a_s + tt * a_stride,
+                       v_s + tt * dv);
+  };
 
   float* st = p.state + ((size_t)p.seq_slot[seq] * p.H + head) * (size_t)dkp * dv;
   float s[KPT], u[KPT];
@@ -78,85 +186,18 @@ __global__ void __launch_bounds__(LS_THREADS) linear_state_kernel(const LinearSt
     u[m] = (MODE == 1 && i < dk) ? p.bonus[(size_t)head * dk + i] : 0.f;
   }
 
-  for (int t0 = 0; t0 < n_tok; t0 += p.tile) {
-    const int cnt = min(p.tile, n_tok - t0);
-    __syncthreads();  // the tile before this one has been used up
-    for (int tt = warp; tt < cnt; tt += LS_THREADS / 32) {
-      const size_t row = (size_t)(first + t0 + tt);
-      float ssq = 0.f, ssk = 0.f;
-      for (int i = lane; i < dkp; i += 32) {
-        float qv = 0.f, kv = 0.f, av = 0.f;
-        if (i < dk) {
-          qv = parts_sum(p.q.p, p.q.n, p.q.stride, row * p.q.width + p.q.off + (size_t)kvh * dk + i);
-          kv = parts_sum(p.k.p, p.k.n, p.k.stride, row * p.k.width + p.k.off + (size_t)kvh * dk + i);
-          if (MODE != 2) av = p.decay[row * p.decay_width + p.decay_off + (size_t)head * dk + i];
-        }
-        ssq = fmaf(qv, qv, ssq);
-        ssk = fmaf(kv, kv, ssk);
-        q_s[tt * dkp + i] = qv;
-        k_s[tt * dkp + i] = kv;
-        if (MODE != 2) a_s[tt * dkp + i] = av;
-      }
-      float qmul = p.q_scale, kmul = 1.0f;
-      if (MODE == 2) {
-        ssq = warp_sum(ssq);
-        ssk = warp_sum(ssk);
-        if (p.unit_eps >= 0.f) {
-          qmul = p.q_scale / sqrtf(ssq + p.unit_eps);
-          kmul = 1.0f / sqrtf(ssk + p.unit_eps);
-        }
-        if (lane == 0) {
-          a_s[tt * 2] = p.decay[row * p.decay_width + p.decay_off + head];
-          a_s[tt * 2 + 1] = p.decay[row * p.decay_width + p.decay_off + p.H + head];
-        }
-      }
-      for (int i = lane; i < dkp; i += 32) {  // the lane's own numbers again
-        q_s[tt * dkp + i] *= qmul;
-        if (MODE == 2) k_s[tt * dkp + i] *= kmul;
-      }
-      for (int j = lane; j < dv; j += 32)
-        v_s[tt * dv + j] = parts_sum(p.v.p, p.v.n, p.v.stride, row * p.v.width + p.v.off + (size_t)head * dv + j);
+  fetch(0, 0, warp, LS_BLOCK / 32);
+  __syncthreads();
+  for (int t0 = 0, buf = 0; t0 < n_tok; t0 += p.tile, buf ^= 1) {
+    if (walker) {
+      float *q_s, *k_s, *a_s, *v_s;
+      rows_of(buf, q_s, k_s, a_s, v_s);
+      walk_tile<MODE>(s, u, q_s, k_s, a_s, a_stride, v_s, dv, col, min(p.tile, n_tok - t0), dkp, R, lane_r, live,
+                      p.out + (size_t)(first + t0) * p.H * dv + (size_t)head * dv + col, (size_t)p.H * dv);
+    } else if (t0 + p.tile < n_tok) {
+      fetch(t0 + p.tile, buf ^ 1, warp - LS_THREADS / 32, (LS_BLOCK - LS_THREADS) / 32);
     }
-    __syncthreads();
-    for (int tt = 0; tt < cnt; ++tt) {
-      const float* qt = q_s + tt * dkp + lane_r;
-      const float* kt = k_s + tt * dkp + lane_r;
-      const float vj = live ? v_s[tt * dv + col] : 0.f;
-      float acc = 0.f;
-      if (MODE == 0) {
-        const float* at = a_s + tt * dkp + lane_r;
-#pragma unroll
-        for (int m = 0; m < KPT; ++m) {
-          s[m] = fmaf(kt[R * m], vj, at[R * m] * s[m]);
-          acc = fmaf(s[m], qt[R * m], acc);
-        }
-      } else if (MODE == 1) {
-        const float* at = a_s + tt * dkp + lane_r;
-#pragma unroll
-        for (int m = 0; m < KPT; ++m) {
-          const float kv = kt[R * m] * vj;
-          acc = fmaf(fmaf(u[m], kv, s[m]), qt[R * m], acc);
-          s[m] = fmaf(at[R * m], s[m], kv);
-        }
-      } else {
-        const float g = a_s[tt * 2], beta = a_s[tt * 2 + 1];
-        float dot = 0.f;
-#pragma unroll
-        for (int m = 0; m < KPT; ++m) {
-          s[m] *= g;
-          dot = fmaf(s[m], kt[R * m], dot);
-        }
-        for (int o = R >> 1; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-        const float w = beta * (vj - dot);
-#pragma unroll
-        for (int m = 0; m < KPT; ++m) {
-          s[m] = fmaf(kt[R * m], w, s[m]);
-          acc = fmaf(s[m], qt[R * m], acc);
-        }
-      }
-      for (int o = R >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (live && lane_r == 0) p.out[(size_t)(first + t0 + tt) * p.H * dv + (size_t)head * dv + col] = acc;
-    }
+    __syncthreads();  // the tile has been used up, the next one is in place
   }
   if (live) {
 #pragma unroll
@@ -269,14 +310,14 @@ extern "C" int llm_linear_state(int mode, const float* q, int qn, long long qs, 
   p.seq_qoff = seq_qoff; p.seq_ntok = seq_ntok; p.seq_slot = seq_slot; p.out = out;
   p.H = H; p.G = G; p.dk = dk; p.dv = dv; p.R = lanes_for(dk); p.q_scale = q_scale; p.unit_eps = unit_eps;
   const int dkp = p.R * KPT;
-  auto smem_for = [&](int tile) { return (size_t)tile * ((mode == 2 ? 2 * dkp + 2 : 3 * dkp) + dv) * sizeof(float); };
+  auto smem_for = [&](int tile) { return 2 * (size_t)tile * ((mode == 2 ? 2 * dkp + 2 : 3 * dkp) + dv) * sizeof(float); };  // two buffers
   p.tile = 16;
   while (p.tile > 1 && smem_for(p.tile) > 48 * 1024) p.tile /= 2;
   LLM_REQUIRE(smem_for(p.tile) <= 48 * 1024, "linear_state: heads of %d / %d numbers exceed one block's shared memory", dk, dv);
   dim3 grid(ceil_div(dv, LS_THREADS / p.R), H, n_seqs);
-  if (mode == 0) launch_kernel(linear_state_kernel<0>, grid, LS_THREADS, smem_for(p.tile), stream, p);
-  else if (mode == 1) launch_kernel(linear_state_kernel<1>, grid, LS_THREADS, smem_for(p.tile), stream, p);
-  else launch_kernel(linear_state_kernel<2>, grid, LS_THREADS, smem_for(p.tile), stream, p);
+  if (mode == 0) launch_kernel(linear_state_kernel<0>, grid, LS_BLOCK, smem_for(p.tile), stream, p);
+  else if (mode == 1) launch_kernel(linear_state_kernel<1>, grid, LS_BLOCK, smem_for(p.tile), stream, p);
+  else launch_kernel(linear_state_kernel<2>, grid, LS_BLOCK, smem_for(p.tile), stream, p);
   LLM_CHECK_LAUNCH("linear_state");
   return LLM_OK;
 }

@@ -237,7 +237,7 @@ class CudaOps:
                                      c_int(block), *self._act_args(act), _stream()), lib)
         return out
 
-    EPILOGUE_ACTIVATIONS = ("silu", "gelu_tanh")  # what the gate|up product applies in its own epilogue (gemm_swiglu)
+    EPILOGUE_ACTIVATIONS = ("silu", "gelu_tanh", "clamped_swish")  # what the gate|up product applies in its own epilogue (gemm_swiglu)
 
     def gemm_swiglu(self, a: torch.Tensor, w_blocked: torch.Tensor, out: torch.Tensor, ws=None,
                     row_scale: Optional[RowScale] = None, act: str = "silu") -> torch.Tensor:
@@ -249,12 +249,12 @@ class CudaOps:
         m, k = a.shape
         ff = out.shape[1]
         assert w_blocked.shape == (2 * ff, k) and out.shape[0] == m and out.is_contiguous() and ff % 128 == 0
-        if m > self.SWAP_MAX_TOKENS and act in self.EPILOGUE_ACTIVATIONS and self._tc_usable(a, w_blocked):
+        if m > self.SWAP_MAX_TOKENS and (act[0] if isinstance(act, tuple) else act) in self.EPILOGUE_ACTIVATIONS and self._tc_usable(a, w_blocked):
             assert row_scale is None, "a row scale is applied where partial sums are consumed (few tokens)"
             lib = self.lib("tensorcore")
             self._check(lib.llm_gemm_tc_swiglu(_ptr(a), _ptr(w_blocked), _ptr(out), c_int(m), c_int(ff), c_int(k),
                                                c_longlong(a.stride(0)), c_longlong(w_blocked.stride(0)),
-                                               c_longlong(out.stride(0)), c_int(self.ACTIVATIONS[act]), _stream()), lib)
+                                               c_longlong(out.stride(0)), *self._act_args(act), _stream()), lib)
             return out
         assert ws is not None, "gemm_swiglu needs a workspace when it cannot fuse"
         if m <= self.SWAP_MAX_TOKENS:

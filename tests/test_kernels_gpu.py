@@ -143,6 +143,25 @@ def test_gemm_with_fused_swiglu(ops, M, FF, K):
     assert ops.tensor_core_error() == 0
 
 
+@pytest.mark.parametrize("M", [9, 70, 300, 2304])
+@pytest.mark.parametrize("FF,K,limit,slope", [(128, 64, 0.5, 1.702), (1024, 512, 2.0, 1.0), (2304, 256, 1.25, 2.5)])
+def test_gemm_with_fused_clamped_swish(ops, M, FF, K, limit, slope):
+    """min(g, L) * sigmoid(s * min(g, L)) * (clamp(u, -L, L) + 1) from the product's epilogue in each of its forms (a tile a
+    block, persistent, block pairs) and from partial sums (few tokens); gates and ups lie beyond the limit on both sides."""
+    from llmengine.engine.context import Workspace
+    a = rnd(M, K, dtype=torch.bfloat16, seed=63)
+    g, u = rnd(FF, K, dtype=torch.bfloat16, seed=64, std=0.2), rnd(FF, K, dtype=torch.bfloat16, seed=65, std=0.2)
+    blocked = torch.stack([g.view(-1, 128, K), u.view(-1, 128, K)], dim=1).reshape(2 * FF, K).contiguous()
+    out = torch.full((M, FF), float("nan"), dtype=torch.bfloat16, device=DEV)
+    ops.gemm_swiglu(a, blocked, out, Workspace(torch.device(DEV)), act=("clamped_swish", limit, slope))
+    gf, uf = (a.double() @ g.double().t()).cpu(), (a.double() @ u.double().t()).cpu()
+    assert (gf > limit).any() and (gf < -limit).any() and (uf > limit).any() and (uf < -limit).any()
+    gc = gf.clamp(max=limit)
+    ref = gc * torch.sigmoid(slope * gc) * (uf.clamp(-limit, limit) + 1.0)
+    torch.testing.assert_close(out.double().cpu(), ref, **tol(torch.bfloat16))
+    assert ops.tensor_core_error() == 0
+
+
 @pytest.fixture
 def one_cta_products(ops):
     """No CTA pairs during the test: it is about the kernels that give a tile to one CTA."""
