@@ -14,7 +14,7 @@
 // steps, on the batch or on the slot: the same additions happen in the same order.
 //
 // In the slot a head's matrix is stored as the threads hold it: number (m, column j, lane r) at ((m * dv + j) * R + r), which is
-// S[r + R * m, j]; loads and stores of a warp are then 128 contiguous bytes. R = the power of two >= dk / 16.
+// S[channel_of(m, r, R), j]; loads and stores of a warp are then 128 contiguous bytes. R = the power of two >= dk / 16.
 //
 // Beside it: token_shift (every projection's own blend of a token's input with the previous token's, the previous token of a
 // portion's first token coming from the slot), delta_gates (the delta rule's decay and write strength per head) and
@@ -50,6 +50,18 @@ struct LinearStateParams {
   float q_scale, unit_eps;
 };
 
+// Key channel of a lane's number m: the lane holds four groups of four neighbouring channels, group c of lane r being channels
+// 4 (c R + r) .. + 3, so that a lane reads a group with one 16-byte load and the R lanes of a column read 16 R contiguous bytes.
+__device__ __forceinline__ int channel_of(int m, int lane_r, int R) { return (((m >> 2) * R + lane_r) << 2) + (m & 3); }
+
+__device__ __forceinline__ void load16(float (&x)[KPT], const float* __restrict__ row, int R) {
+#pragma unroll
+  for (int c = 0; c < KPT / 4; ++c) {
+    const float4 t = *reinterpret_cast<const float4*>(row + 4 * c * R);
+    x[4 * c] = t.x; x[4 * c + 1] = t.y; x[4 * c + 2] = t.z; x[4 * c + 3] = t.w;
+  }
+}
+
 // A tile of tokens through the rule: s the thread's numbers of its column, q_s / k_s / a_s the tile's rows in shared memory,
 // v_s[tt * v_stride + v_idx] the column's value; out points at the column's result of the tile's first token. A lane's sixteen
 // products are summed as four interleaved chains ((c0 + c1) + (c2 + c3), chain i taking m = i, i + 4, ...), which shortens the
@@ -60,24 +72,27 @@ __device__ __forceinline__ void walk_tile(float (&s)[KPT], const float (&u)[KPT]
                                           int cnt, int dkp, int R, int lane_r, bool live, float* __restrict__ out, size_t out_stride) {
 #pragma unroll 2
   for (int tt = 0; tt < cnt; ++tt) {
-    const float* qt = q_s + tt * dkp + lane_r;
-    const float* kt = k_s + tt * dkp + lane_r;
+    float qq[KPT], kk[KPT];
+    load16(kk, k_s + tt * dkp + 4 * lane_r, R);
+    load16(qq, q_s + tt * dkp + 4 * lane_r, R);
     const float vj = live ? v_s[tt * v_stride + v_idx] : 0.f;
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     if (MODE == 0) {
-      const float* at = a_s + tt * a_stride + lane_r;
+      float aa[KPT];
+      load16(aa, a_s + tt * a_stride + 4 * lane_r, R);
 #pragma unroll
       for (int m = 0; m < KPT; ++m) {
-        s[m] = fmaf(kt[R * m], vj, at[R * m] * s[m]);
-        acc[m & 3] = fmaf(s[m], qt[R * m], acc[m & 3]);
+        s[m] = fmaf(kk[m], vj, aa[m] * s[m]);
+        acc[m & 3] = fmaf(s[m], qq[m], acc[m & 3]);
       }
     } else if (MODE == 1) {
-      const float* at = a_s + tt * a_stride + lane_r;
+      float aa[KPT];
+      load16(aa, a_s + tt * a_stride + 4 * lane_r, R);
 #pragma unroll
       for (int m = 0; m < KPT; ++m) {
-        const float kv = kt[R * m] * vj;
-        acc[m & 3] = fmaf(fmaf(u[m], kv, s[m]), qt[R * m], acc[m & 3]);
-        s[m] = fmaf(at[R * m], s[m], kv);
+        const float kv = kk[m] * vj;
+        acc[m & 3] = fmaf(fmaf(u[m], kv, s[m]), qq[m], acc[m & 3]);
+        s[m] = fmaf(aa[m], s[m], kv);
       }
     } else {
       const float g = a_s[tt * a_stride], beta = a_s[tt * a_stride + 1];
@@ -85,15 +100,15 @@ __device__ __forceinline__ void walk_tile(float (&s)[KPT], const float (&u)[KPT]
 #pragma unroll
       for (int m = 0; m < KPT; ++m) {
         s[m] *= g;
-        dot[m & 3] = fmaf(s[m], kt[R * m], dot[m & 3]);
+        dot[m & 3] = fmaf(s[m], kk[m], dot[m & 3]);
       }
       float d = (dot[0] + dot[1]) + (dot[2] + dot[3]);
       for (int o = R >> 1; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
       const float w = beta * (vj - d);
 #pragma unroll
       for (int m = 0; m < KPT; ++m) {
-        s[m] = fmaf(kt[R * m], w, s[m]);
-        acc[m & 3] = fmaf(s[m], qt[R * m], acc[m & 3]);
+        s[m] = fmaf(kk[m], w, s[m]);
+        acc[m & 3] = fmaf(s[m], qq[m], acc[m & 3]);
       }
     }
     float r = (acc[0] + acc[1]) + (acc[2] + acc[3]);
@@ -102,51 +117,132 @@ __device__ __forceinline__ void walk_tile(float (&s)[KPT], const float (&u)[KPT]
   }
 }
 
-// One token's row into a tile's shared memory, by one warp: the sums of the products' parts, the unit norms and the query's scale.
+__device__ __forceinline__ void copy4_async(float* smem_dst, const float* gmem_src) {
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void copies_wait() { asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory"); }
+
+// A tile's rows into shared memory by the n_thr fetching threads (thread `tid` of them): every thread takes elements of the
+// whole tile in turn. Products in one part (a prompt's portion) are copied asynchronously, all of a tile's copies in flight
+// at once and no registers held, so a tile costs one trip to memory; the thread then scales its own queries. Products in
+// several parts (few tokens, K cut) go through registers, a few elements at a time, the parts added in their order. The delta
+// rule's unit norms need a token's whole row: the fetchers meet (barrier 1 is theirs alone) and a warp a token scales what
+// was stored.
 template <int MODE>
-__device__ __forceinline__ void load_token(const LinearStateParams& p, size_t row, int head, int kvh, int dk, int dkp, int dv, int lane,
-                                           float* __restrict__ q_row, float* __restrict__ k_row, float* __restrict__ a_row,
-                                           float* __restrict__ v_row) {
-  float ssq = 0.f, ssk = 0.f;
-  for (int i = lane; i < dkp; i += 32) {
-    float qv = 0.f, kv = 0.f, av = 0.f;
-    if (i < dk) {
-      qv = parts_sum(p.q.p, p.q.n, p.q.stride, row * p.q.width + p.q.off + (size_t)kvh * dk + i);
-      kv = parts_sum(p.k.p, p.k.n, p.k.stride, row * p.k.width + p.k.off + (size_t)kvh * dk + i);
-      if (MODE != 2) av = p.decay[row * p.decay_width + p.decay_off + (size_t)head * dk + i];
+__device__ __forceinline__ void fetch_tile(const LinearStateParams& p, size_t row0, int cnt, int head, int kvh, int dk, int dkp, int dv,
+                                           int tid, int n_thr, float* __restrict__ q_s, float* __restrict__ k_s, float* __restrict__ a_s,
+                                           float* __restrict__ v_s) {
+  const bool unit = MODE == 2 && p.unit_eps >= 0.f;
+  const float qmul = unit ? 1.0f : p.q_scale;
+  const int n_qk = cnt * dkp, n_v = cnt * dv;
+  if (p.q.n == 1 && p.k.n == 1 && p.v.n == 1) {
+    for (int e = tid; e < n_qk; e += n_thr) {
+      const int tt = e / dkp, i = e - tt * dkp;
+      const size_t row = row0 + tt;
+      if (i < dk) {
+        copy4_async(q_s + e, p.q.p + row * p.q.width + p.q.off + (size_t)kvh * dk + i);
+        copy4_async(k_s + e, p.k.p + row * p.k.width + p.k.off + (size_t)kvh * dk + i);
+        if (MODE != 2) copy4_async(a_s + e, p.decay + row * p.decay_width + p.decay_off + (size_t)head * dk + i);
+      } else {
+        q_s[e] = k_s[e] = 0.f;
+        if (MODE != 2) a_s[e] = 0.f;
+      }
     }
-    ssq = fmaf(qv, qv, ssq);
-    ssk = fmaf(kv, kv, ssk);
-    q_row[i] = qv;
-    k_row[i] = kv;
-    if (MODE != 2) a_row[i] = av;
+    for (int e = tid; e < n_v; e += n_thr) {
+      const int tt = e / dv, j = e - tt * dv;
+      copy4_async(v_s + e, p.v.p + (row0 + tt) * p.v.width + p.v.off + (size_t)head * dv + j);
+    }
+    if (MODE == 2)
+      for (int e = tid; e < 2 * cnt; e += n_thr)
+        copy4_async(a_s + e, p.decay + (row0 + (e >> 1)) * p.decay_width + p.decay_off + (e & 1) * p.H + head);
+    copies_wait();
+    if (qmul != 1.0f)
+      for (int e = tid; e < n_qk; e += n_thr) q_s[e] *= qmul;  // the thread's own copies
+  } else {
+    constexpr int U = 4;  // elements a thread has in flight: their loads are issued together, part after part in the parts' order
+  for (int e0 = tid; e0 < n_qk; e0 += U * n_thr) {
+    float qv[U], kv[U], av[U];
+    size_t qi[U], ki[U];
+    bool ok[U];
+#pragma unroll
+    for (int x = 0; x < U; ++x) {
+      const int e = e0 + x * n_thr, tt = e / dkp, i = e - tt * dkp;
+      const size_t row = row0 + tt;
+      ok[x] = e < n_qk && i < dk;
+      qi[x] = row * p.q.width + p.q.off + (size_t)kvh * dk + i;
+      ki[x] = row * p.k.width + p.k.off + (size_t)kvh * dk + i;
+      qv[x] = kv[x] = 0.f;
+      av[x] = (MODE != 2 && ok[x]) ? p.decay[row * p.decay_width + p.decay_off + (size_t)head * dk + i] : 0.f;
+    }
+    for (int part = 0; part < p.q.n; ++part) {
+#pragma unroll
+      for (int x = 0; x < U; ++x)
+        if (ok[x]) qv[x] += p.q.p[(size_t)part * p.q.stride + qi[x]];
+    }
+    for (int part = 0; part < p.k.n; ++part) {
+#pragma unroll
+      for (int x = 0; x < U; ++x)
+        if (ok[x]) kv[x] += p.k.p[(size_t)part * p.k.stride + ki[x]];
+    }
+#pragma unroll
+    for (int x = 0; x < U; ++x) {
+      const int e = e0 + x * n_thr;
+      if (e < n_qk) {
+        q_s[e] = qv[x] * qmul;
+        k_s[e] = kv[x];
+        if (MODE != 2) a_s[e] = av[x];
+      }
+    }
   }
-  for (int j = lane; j < dv; j += 32) v_row[j] = parts_sum(p.v.p, p.v.n, p.v.stride, row * p.v.width + p.v.off + (size_t)head * dv + j);
-  float qmul = p.q_scale, kmul = 1.0f;
+  for (int e0 = tid; e0 < n_v; e0 += U * n_thr) {
+    float vv[U];
+    size_t vi[U];
+#pragma unroll
+    for (int x = 0; x < U; ++x) {
+      const int e = min(e0 + x * n_thr, n_v - 1), tt = e / dv, j = e - tt * dv;
+      vi[x] = (row0 + tt) * p.v.width + p.v.off + (size_t)head * dv + j;
+      vv[x] = 0.f;
+    }
+    for (int part = 0; part < p.v.n; ++part) {
+#pragma unroll
+      for (int x = 0; x < U; ++x) vv[x] += p.v.p[(size_t)part * p.v.stride + vi[x]];
+    }
+#pragma unroll
+    for (int x = 0; x < U; ++x)
+      if (e0 + x * n_thr < n_v) v_s[e0 + x * n_thr] = vv[x];
+  }
+    if (MODE == 2)
+      for (int e = tid; e < 2 * cnt; e += n_thr) a_s[e] = p.decay[(row0 + (e >> 1)) * p.decay_width + p.decay_off + (e & 1) * p.H + head];
+  }
   if (MODE == 2) {
-    ssq = warp_sum(ssq);
-    ssk = warp_sum(ssk);
-    if (p.unit_eps >= 0.f) {
-      qmul = p.q_scale / sqrtf(ssq + p.unit_eps);
-      kmul = 1.0f / sqrtf(ssk + p.unit_eps);
+    if (unit) {
+      asm volatile("bar.sync 1, %0;" ::"r"(n_thr) : "memory");
+      const int lane = tid & 31;
+      for (int tt = tid >> 5; tt < cnt; tt += n_thr >> 5) {
+        float ssq = 0.f, ssk = 0.f;
+        for (int i = lane; i < dkp; i += 32) {
+          ssq = fmaf(q_s[tt * dkp + i], q_s[tt * dkp + i], ssq);
+          ssk = fmaf(k_s[tt * dkp + i], k_s[tt * dkp + i], ssk);
+        }
+        ssq = warp_sum(ssq);
+        ssk = warp_sum(ssk);
+        const float qm = p.q_scale / sqrtf(ssq + p.unit_eps), km = 1.0f / sqrtf(ssk + p.unit_eps);
+        for (int i = lane; i < dkp; i += 32) {  // the lane's own numbers again
+          q_s[tt * dkp + i] *= qm;
+          k_s[tt * dkp + i] *= km;
+        }
+      }
     }
-    if (lane == 0) {
-      a_row[0] = p.decay[row * p.decay_width + p.decay_off + head];
-      a_row[1] = p.decay[row * p.decay_width + p.decay_off + p.H + head];
-    }
-  }
-  for (int i = lane; i < dkp; i += 32) {  // the lane's own numbers again
-    q_row[i] *= qmul;
-    if (MODE == 2) k_row[i] *= kmul;
   }
 }
 
 // Threads 0 .. LS_THREADS - 1 hold the state and walk; the warps behind them only fetch: while the walkers are in tile i of
-// the request's tokens, the fetchers fill the other buffer with tile i + 1, and the block meets once a tile. (The first tile is
-// fetched by all warps; a decode step has only that one.)
+// the request's tokens, the fetchers fill the other buffer with tile i + 1, and the block meets once a tile. (A decode step
+// has one tile of one token; the walkers read their state while it is fetched.)
 template <int MODE>
-__global__ void __launch_bounds__(LS_BLOCK) linear_state_kernel(const LinearStateParams p) {
-  extern __shared__ float sh_ls[];
+__global__ void __launch_bounds__(LS_BLOCK, 1) linear_state_kernel(const LinearStateParams p) {
+  extern __shared__ __align__(16) float sh_ls[];
   dep_launch();
   dep_wait();
   const int seq = blockIdx.z, head = blockIdx.y, R = p.R, dk = p.dk, dv = p.dv;
@@ -159,22 +255,19 @@ __global__ void __launch_bounds__(LS_BLOCK) linear_state_kernel(const LinearStat
   const int lane_r = threadIdx.x & (R - 1);
   const int col = blockIdx.x * (LS_THREADS / R) + threadIdx.x / R;
   const bool live = walker && col < dv;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int a_stride = MODE == 2 ? 2 : dkp;
-  const size_t buf_floats = (size_t)p.tile * (2 * dkp + a_stride + dv);
+  const size_t buf_floats = ((size_t)p.tile * (2 * dkp + a_stride + dv) + 3) & ~(size_t)3;  // buffers start on 16 bytes
   auto rows_of = [&](int buf, float*& q_s, float*& k_s, float*& a_s, float*& v_s) {
     q_s = sh_ls + (size_t)buf * buf_floats;  // [tile][dkp]
     k_s = q_s + (size_t)p.tile * dkp;        // [tile][dkp]
     a_s = k_s + (size_t)p.tile * dkp;        // [tile][dkp] (MODE 0/1) or [tile][2] (MODE 2)
     v_s = a_s + (size_t)p.tile * a_stride;   // [tile][dv]
   };
-  auto fetch = [&](int t0, int buf, int w, int n_w) {
+  auto fetch = [&](int t0, int buf) {
     float *q_s, *k_s, *a_s, *v_s;
     rows_of(buf, q_s, k_s, a_s, v_s);
-    const int cnt = min(p.tile, n_tok - t0);
-    for (int tt = w; tt < cnt; tt += n_w)
-      load_token<MODE>(p, (size_t)(first + t0 + tt), head, kvh, dk, dkp, dv, lane, q_s + tt * dkp, k_s + tt * dkp, a_s + tt * a_stride,
-                       v_s + tt * dv);
+    fetch_tile<MODE>(p, (size_t)(first + t0), min(p.tile, n_tok - t0), head, kvh, dk, dkp, dv, threadIdx.x - LS_THREADS,
+                     LS_BLOCK - LS_THREADS, q_s, k_s, a_s, v_s);
   };
 
   float* st = p.state + ((size_t)p.seq_slot[seq] * p.H + head) * (size_t)dkp * dv;
@@ -182,11 +275,11 @@ __global__ void __launch_bounds__(LS_BLOCK) linear_state_kernel(const LinearStat
 #pragma unroll
   for (int m = 0; m < KPT; ++m) {
     s[m] = live ? st[((size_t)m * dv + col) * R + lane_r] : 0.f;
-    const int i = lane_r + R * m;
+    const int i = channel_of(m, lane_r, R);
     u[m] = (MODE == 1 && i < dk) ? p.bonus[(size_t)head * dk + i] : 0.f;
   }
 
-  fetch(0, 0, warp, LS_BLOCK / 32);
+  if (!walker) fetch(0, 0);
   __syncthreads();
   for (int t0 = 0, buf = 0; t0 < n_tok; t0 += p.tile, buf ^= 1) {
     if (walker) {
@@ -195,7 +288,7 @@ __global__ void __launch_bounds__(LS_BLOCK) linear_state_kernel(const LinearStat
       walk_tile<MODE>(s, u, q_s, k_s, a_s, a_stride, v_s, dv, col, min(p.tile, n_tok - t0), dkp, R, lane_r, live,
                       p.out + (size_t)(first + t0) * p.H * dv + (size_t)head * dv + col, (size_t)p.H * dv);
     } else if (t0 + p.tile < n_tok) {
-      fetch(t0 + p.tile, buf ^ 1, warp - LS_THREADS / 32, (LS_BLOCK - LS_THREADS) / 32);
+      fetch(t0 + p.tile, buf ^ 1);
     }
     __syncthreads();  // the tile has been used up, the next one is in place
   }
@@ -310,7 +403,7 @@ extern "C" int llm_linear_state(int mode, const float* q, int qn, long long qs, 
   p.seq_qoff = seq_qoff; p.seq_ntok = seq_ntok; p.seq_slot = seq_slot; p.out = out;
   p.H = H; p.G = G; p.dk = dk; p.dv = dv; p.R = lanes_for(dk); p.q_scale = q_scale; p.unit_eps = unit_eps;
   const int dkp = p.R * KPT;
-  auto smem_for = [&](int tile) { return 2 * (size_t)tile * ((mode == 2 ? 2 * dkp + 2 : 3 * dkp) + dv) * sizeof(float); };  // two buffers
+  auto smem_for = [&](int tile) { return 2 * (((size_t)tile * ((mode == 2 ? 2 * dkp + 2 : 3 * dkp) + dv) + 3) & ~(size_t)3) * sizeof(float); };  // two buffers
   p.tile = 16;
   while (p.tile > 1 && smem_for(p.tile) > 48 * 1024) p.tile /= 2;
   LLM_REQUIRE(smem_for(p.tile) <= 48 * 1024, "linear_state: heads of %d / %d numbers exceed one block's shared memory", dk, dv);
