@@ -27,7 +27,8 @@ namespace {
 
 constexpr int KPT = 16;       // state numbers of a column that one lane holds
 constexpr int LS_THREADS = 128;  // threads that hold the state
-constexpr int LS_BLOCK = 256;    // with the warps that fetch the next tile of tokens
+constexpr int LS_BLOCK = 256;    // with the warps that fetch the tiles of tokens ahead
+constexpr int LS_BUFFERS = 3;    // tiles in shared memory: walked, landing, issued
 
 __device__ __forceinline__ float parts_sum(const float* __restrict__ p, int n_parts, size_t pstride, size_t i) {
   float s = p[i];
@@ -48,13 +49,16 @@ struct LinearStateParams {
   float* out;                                      // [tokens, H * dv]
   int H, G, dk, dv, R, tile;
   float q_scale, unit_eps;
+  int one_part;  // every product comes in one part
+  int vec4;      // every row and column offset is a multiple of four numbers on a 16-byte boundary
 };
 
 // Key channel of a lane's number m: the lane holds four groups of four neighbouring channels, group c of lane r being channels
 // 4 (c R + r) .. + 3, so that a lane reads a group with one 16-byte load and the R lanes of a column read 16 R contiguous bytes.
 __device__ __forceinline__ int channel_of(int m, int lane_r, int R) { return (((m >> 2) * R + lane_r) << 2) + (m & 3); }
 
-__device__ __forceinline__ void load16(float (&x)[KPT], const float* __restrict__ row, int R) {
+template <int R>
+__device__ __forceinline__ void load16(float (&x)[KPT], const float* __restrict__ row) {
 #pragma unroll
   for (int c = 0; c < KPT / 4; ++c) {
     const float4 t = *reinterpret_cast<const float4*>(row + 4 * c * R);
@@ -62,32 +66,55 @@ __device__ __forceinline__ void load16(float (&x)[KPT], const float* __restrict_
   }
 }
 
-// A tile of tokens through the rule: s the thread's numbers of its column, q_s / k_s / a_s the tile's rows in shared memory,
-// v_s[tt * v_stride + v_idx] the column's value; out points at the column's result of the tile's first token. A lane's sixteen
-// products are summed as four interleaved chains ((c0 + c1) + (c2 + c3), chain i taking m = i, i + 4, ...), which shortens the
-// dependent chain of a token fourfold; the order is fixed, so a token's result is the same in every step that computes it.
-template <int MODE>
-__device__ __forceinline__ void walk_tile(float (&s)[KPT], const float (&u)[KPT], const float* __restrict__ q_s, const float* __restrict__ k_s,
-                                          const float* __restrict__ a_s, int a_stride, const float* __restrict__ v_s, int v_stride, int v_idx,
-                                          int cnt, int dkp, int R, int lane_r, bool live, float* __restrict__ out, size_t out_stride) {
+template <int R>
+__device__ __forceinline__ float lanes_sum(float x) {  // over the R lanes of a column, a fixed order
+#pragma unroll
+  for (int o = R >> 1; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+  return x;
+}
+
+struct TileRows {  // a tile of tokens in shared memory
+  float* q;  // [tile][dkp]
+  float* k;  // [tile][dkp]
+  float* a;  // [tile][dkp] (MODE 0/1) or [tile][2] (MODE 2)
+  float* v;  // [tile][dv]
+};
+
+// A tile of tokens through the rule: s the thread's numbers of its column, v[tt * dv + col] the column's value; out points at the
+// column's result of the tile's first token. A lane's sixteen products are summed as four interleaved chains ((c0 + c1) +
+// (c2 + c3), chain i taking m = i, i + 4, ...), which shortens the dependent chain of a token fourfold; the order is fixed, so a
+// token's result is the same in every step that computes it. What the state does not wait for is moved out of its way: the next
+// token's rows are read while this one is computed, and a result's sum over the lanes and its store happen one token late.
+template <int MODE, int R>
+__device__ __forceinline__ void walk_tile(float (&s)[KPT], const float (&u)[KPT], const TileRows& rows, int dv, int col, int cnt, int lane_r,
+                                          bool live, float* __restrict__ out, size_t out_stride) {
+  constexpr int dkp = R * KPT, a_stride = MODE == 2 ? 2 : dkp;
+  float kk[KPT], qq[KPT], aa[KPT], vj, g = 0.f, beta = 0.f;
+  auto read = [&](int tt, float (&k_)[KPT], float (&q_)[KPT], float (&a_)[KPT], float& v_, float& g_, float& b_) {
+    load16<R>(k_, rows.k + tt * dkp + 4 * lane_r);
+    load16<R>(q_, rows.q + tt * dkp + 4 * lane_r);
+    if (MODE != 2) {
+      load16<R>(a_, rows.a + tt * a_stride + 4 * lane_r);
+    } else {
+      g_ = rows.a[tt * a_stride];
+      b_ = rows.a[tt * a_stride + 1];
+    }
+    v_ = live ? rows.v[tt * dv + col] : 0.f;
+  };
+  read(0, kk, qq, aa, vj, g, beta);
+  float pend = 0.f;
 #pragma unroll 2
   for (int tt = 0; tt < cnt; ++tt) {
-    float qq[KPT], kk[KPT];
-    load16(kk, k_s + tt * dkp + 4 * lane_r, R);
-    load16(qq, q_s + tt * dkp + 4 * lane_r, R);
-    const float vj = live ? v_s[tt * v_stride + v_idx] : 0.f;
+    float kn[KPT], qn[KPT], an[KPT], vn, gn = 0.f, bn = 0.f;
+    read(min(tt + 1, cnt - 1), kn, qn, an, vn, gn, bn);
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     if (MODE == 0) {
-      float aa[KPT];
-      load16(aa, a_s + tt * a_stride + 4 * lane_r, R);
 #pragma unroll
       for (int m = 0; m < KPT; ++m) {
         s[m] = fmaf(kk[m], vj, aa[m] * s[m]);
         acc[m & 3] = fmaf(s[m], qq[m], acc[m & 3]);
       }
     } else if (MODE == 1) {
-      float aa[KPT];
-      load16(aa, a_s + tt * a_stride + 4 * lane_r, R);
 #pragma unroll
       for (int m = 0; m < KPT; ++m) {
         const float kv = kk[m] * vj;
@@ -95,15 +122,13 @@ __device__ __forceinline__ void walk_tile(float (&s)[KPT], const float (&u)[KPT]
         s[m] = fmaf(aa[m], s[m], kv);
       }
     } else {
-      const float g = a_s[tt * a_stride], beta = a_s[tt * a_stride + 1];
       float dot[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int m = 0; m < KPT; ++m) {
         s[m] *= g;
         dot[m & 3] = fmaf(s[m], kk[m], dot[m & 3]);
       }
-      float d = (dot[0] + dot[1]) + (dot[2] + dot[3]);
-      for (int o = R >> 1; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+      const float d = lanes_sum<R>((dot[0] + dot[1]) + (dot[2] + dot[3]));
       const float w = beta * (vj - d);
 #pragma unroll
       for (int m = 0; m < KPT; ++m) {
@@ -111,63 +136,100 @@ __device__ __forceinline__ void walk_tile(float (&s)[KPT], const float (&u)[KPT]
         acc[m & 3] = fmaf(s[m], qq[m], acc[m & 3]);
       }
     }
-    float r = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-    for (int o = R >> 1; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
-    if (live && lane_r == 0) out[(size_t)tt * out_stride] = r;
+    if (tt > 0) {
+      const float o = lanes_sum<R>(pend);
+      if (live && lane_r == 0) out[(size_t)(tt - 1) * out_stride] = o;
+    }
+    pend = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+#pragma unroll
+    for (int m = 0; m < KPT; ++m) {
+      kk[m] = kn[m];
+      qq[m] = qn[m];
+      if (MODE != 2) aa[m] = an[m];
+    }
+    vj = vn; g = gn; beta = bn;
   }
+  const float o = lanes_sum<R>(pend);
+  if (live && lane_r == 0) out[(size_t)(cnt - 1) * out_stride] = o;
 }
 
 __device__ __forceinline__ void copy4_async(float* smem_dst, const float* gmem_src) {
   const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(d), "l"(gmem_src) : "memory");
 }
-__device__ __forceinline__ void copies_wait() { asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory"); }
+__device__ __forceinline__ void copy16_async(float* smem_dst, const float* gmem_src) {  // both on 16-byte boundaries
+  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void copies_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void copies_wait_but_last() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
 
-// A tile's rows into shared memory by the n_thr fetching threads (thread `tid` of them): every thread takes elements of the
-// whole tile in turn. Products in one part (a prompt's portion) are copied asynchronously, all of a tile's copies in flight
-// at once and no registers held, so a tile costs one trip to memory; the thread then scales its own queries. Products in
-// several parts (few tokens, K cut) go through registers, a few elements at a time, the parts added in their order. The delta
-// rule's unit norms need a token's whole row: the fetchers meet (barrier 1 is theirs alone) and a warp a token scales what
-// was stored.
+// A tile's rows into shared memory by the n_thr fetching threads (thread `tid` of them), in two steps so that two tiles can be
+// on their way while a third is walked. fetch_issue: every thread takes elements of the whole tile in turn. Products in one
+// part (a prompt's portion) are copied asynchronously (16 bytes a copy where every address allows it), no registers held, and
+// the copies of a tile are one group. Products in several parts (few tokens, K cut) go through registers, a few elements at a
+// time, the parts added in their order. fetch_finish, once the tile's group has landed: the thread scales its own queries; the
+// delta rule's unit norms need a token's whole row, so the fetchers meet (barrier 1 is theirs alone) and a warp a token
+// scales what was stored.
 template <int MODE>
-__device__ __forceinline__ void fetch_tile(const LinearStateParams& p, size_t row0, int cnt, int head, int kvh, int dk, int dkp, int dv,
-                                           int tid, int n_thr, float* __restrict__ q_s, float* __restrict__ k_s, float* __restrict__ a_s,
-                                           float* __restrict__ v_s) {
+__device__ __forceinline__ void fetch_issue(const LinearStateParams& p, size_t row0, int cnt, int head, int kvh, int dk, int dkp, int dv,
+                                            int tid, int n_thr, const TileRows& rows) {
   const bool unit = MODE == 2 && p.unit_eps >= 0.f;
   const float qmul = unit ? 1.0f : p.q_scale;
+  const int lg = __ffs(dkp) - 1;  // dkp is a power of two
   const int n_qk = cnt * dkp, n_v = cnt * dv;
-  if (p.q.n == 1 && p.k.n == 1 && p.v.n == 1) {
-    for (int e = tid; e < n_qk; e += n_thr) {
-      const int tt = e / dkp, i = e - tt * dkp;
-      const size_t row = row0 + tt;
-      if (i < dk) {
-        copy4_async(q_s + e, p.q.p + row * p.q.width + p.q.off + (size_t)kvh * dk + i);
-        copy4_async(k_s + e, p.k.p + row * p.k.width + p.k.off + (size_t)kvh * dk + i);
-        if (MODE != 2) copy4_async(a_s + e, p.decay + row * p.decay_width + p.decay_off + (size_t)head * dk + i);
-      } else {
-        q_s[e] = k_s[e] = 0.f;
-        if (MODE != 2) a_s[e] = 0.f;
+  if (p.one_part) {
+    if (p.vec4) {
+      for (int e = tid; e < (n_qk >> 2); e += n_thr) {
+        const int tt = e >> (lg - 2), i = (e << 2) & (dkp - 1);
+        const size_t row = row0 + tt;
+        if (i < dk) {
+          copy16_async(rows.q + 4 * e, p.q.p + row * p.q.width + p.q.off + (size_t)kvh * dk + i);
+          copy16_async(rows.k + 4 * e, p.k.p + row * p.k.width + p.k.off + (size_t)kvh * dk + i);
+          if (MODE != 2) copy16_async(rows.a + 4 * e, p.decay + row * p.decay_width + p.decay_off + (size_t)head * dk + i);
+        } else {
+          const float4 z = make_float4(0.f, 0.f, 0.f, 0.f);
+          *reinterpret_cast<float4*>(rows.q + 4 * e) = z;
+          *reinterpret_cast<float4*>(rows.k + 4 * e) = z;
+          if (MODE != 2) *reinterpret_cast<float4*>(rows.a + 4 * e) = z;
+        }
       }
-    }
-    for (int e = tid; e < n_v; e += n_thr) {
-      const int tt = e / dv, j = e - tt * dv;
-      copy4_async(v_s + e, p.v.p + (row0 + tt) * p.v.width + p.v.off + (size_t)head * dv + j);
+      const int dv4 = dv >> 2;
+      for (int e = tid; e < (n_v >> 2); e += n_thr) {
+        const int tt = e / dv4, j = (e - tt * dv4) << 2;
+        copy16_async(rows.v + 4 * e, p.v.p + (row0 + tt) * p.v.width + p.v.off + (size_t)head * dv + j);
+      }
+    } else {
+      for (int e = tid; e < n_qk; e += n_thr) {
+        const int tt = e >> lg, i = e & (dkp - 1);
+        const size_t row = row0 + tt;
+        if (i < dk) {
+          copy4_async(rows.q + e, p.q.p + row * p.q.width + p.q.off + (size_t)kvh * dk + i);
+          copy4_async(rows.k + e, p.k.p + row * p.k.width + p.k.off + (size_t)kvh * dk + i);
+          if (MODE != 2) copy4_async(rows.a + e, p.decay + row * p.decay_width + p.decay_off + (size_t)head * dk + i);
+        } else {
+          rows.q[e] = rows.k[e] = 0.f;
+          if (MODE != 2) rows.a[e] = 0.f;
+        }
+      }
+      for (int e = tid; e < n_v; e += n_thr) {
+        const int tt = e / dv, j = e - tt * dv;
+        copy4_async(rows.v + e, p.v.p + (row0 + tt) * p.v.width + p.v.off + (size_t)head * dv + j);
+      }
     }
     if (MODE == 2)
       for (int e = tid; e < 2 * cnt; e += n_thr)
-        copy4_async(a_s + e, p.decay + (row0 + (e >> 1)) * p.decay_width + p.decay_off + (e & 1) * p.H + head);
-    copies_wait();
-    if (qmul != 1.0f)
-      for (int e = tid; e < n_qk; e += n_thr) q_s[e] *= qmul;  // the thread's own copies
-  } else {
-    constexpr int U = 4;  // elements a thread has in flight: their loads are issued together, part after part in the parts' order
+        copy4_async(rows.a + e, p.decay + (row0 + (e >> 1)) * p.decay_width + p.decay_off + (e & 1) * p.H + head);
+    return;
+  }
+  constexpr int U = 4;  // elements a thread has in flight: their loads are issued together, part after part in the parts' order
   for (int e0 = tid; e0 < n_qk; e0 += U * n_thr) {
     float qv[U], kv[U], av[U];
     size_t qi[U], ki[U];
     bool ok[U];
 #pragma unroll
     for (int x = 0; x < U; ++x) {
-      const int e = e0 + x * n_thr, tt = e / dkp, i = e - tt * dkp;
+      const int e = e0 + x * n_thr, tt = e >> lg, i = e & (dkp - 1);
       const size_t row = row0 + tt;
       ok[x] = e < n_qk && i < dk;
       qi[x] = row * p.q.width + p.q.off + (size_t)kvh * dk + i;
@@ -189,9 +251,9 @@ __device__ __forceinline__ void fetch_tile(const LinearStateParams& p, size_t ro
     for (int x = 0; x < U; ++x) {
       const int e = e0 + x * n_thr;
       if (e < n_qk) {
-        q_s[e] = qv[x] * qmul;
-        k_s[e] = kv[x];
-        if (MODE != 2) a_s[e] = av[x];
+        rows.q[e] = qv[x] * qmul;
+        rows.k[e] = kv[x];
+        if (MODE != 2) rows.a[e] = av[x];
       }
     }
   }
@@ -210,87 +272,114 @@ __device__ __forceinline__ void fetch_tile(const LinearStateParams& p, size_t ro
     }
 #pragma unroll
     for (int x = 0; x < U; ++x)
-      if (e0 + x * n_thr < n_v) v_s[e0 + x * n_thr] = vv[x];
+      if (e0 + x * n_thr < n_v) rows.v[e0 + x * n_thr] = vv[x];
   }
-    if (MODE == 2)
-      for (int e = tid; e < 2 * cnt; e += n_thr) a_s[e] = p.decay[(row0 + (e >> 1)) * p.decay_width + p.decay_off + (e & 1) * p.H + head];
+  if (MODE == 2)
+    for (int e = tid; e < 2 * cnt; e += n_thr) rows.a[e] = p.decay[(row0 + (e >> 1)) * p.decay_width + p.decay_off + (e & 1) * p.H + head];
+}
+
+template <int MODE>
+__device__ __forceinline__ void fetch_finish(const LinearStateParams& p, int cnt, int dk, int dkp, int tid, int n_thr, const TileRows& rows) {
+  const bool unit = MODE == 2 && p.unit_eps >= 0.f;
+  const float qmul = unit ? 1.0f : p.q_scale;
+  if (p.one_part && qmul != 1.0f) {  // the thread's own copies, as fetch_issue dealt them
+    const int n_qk = cnt * dkp;
+    if (p.vec4) {
+      for (int e = tid; e < (n_qk >> 2); e += n_thr) {
+        float4 t = *reinterpret_cast<float4*>(rows.q + 4 * e);
+        t.x *= qmul; t.y *= qmul; t.z *= qmul; t.w *= qmul;
+        *reinterpret_cast<float4*>(rows.q + 4 * e) = t;
+      }
+    } else {
+      for (int e = tid; e < n_qk; e += n_thr) rows.q[e] *= qmul;
+    }
   }
-  if (MODE == 2) {
-    if (unit) {
-      asm volatile("bar.sync 1, %0;" ::"r"(n_thr) : "memory");
-      const int lane = tid & 31;
-      for (int tt = tid >> 5; tt < cnt; tt += n_thr >> 5) {
-        float ssq = 0.f, ssk = 0.f;
-        for (int i = lane; i < dkp; i += 32) {
-          ssq = fmaf(q_s[tt * dkp + i], q_s[tt * dkp + i], ssq);
-          ssk = fmaf(k_s[tt * dkp + i], k_s[tt * dkp + i], ssk);
-        }
-        ssq = warp_sum(ssq);
-        ssk = warp_sum(ssk);
-        const float qm = p.q_scale / sqrtf(ssq + p.unit_eps), km = 1.0f / sqrtf(ssk + p.unit_eps);
-        for (int i = lane; i < dkp; i += 32) {  // the lane's own numbers again
-          q_s[tt * dkp + i] *= qm;
-          k_s[tt * dkp + i] *= km;
-        }
+  if (unit) {
+    asm volatile("bar.sync 1, %0;" ::"r"(n_thr) : "memory");
+    const int lane = tid & 31;
+    for (int tt = tid >> 5; tt < cnt; tt += n_thr >> 5) {
+      float ssq = 0.f, ssk = 0.f;
+      for (int i = lane; i < dkp; i += 32) {
+        ssq = fmaf(rows.q[tt * dkp + i], rows.q[tt * dkp + i], ssq);
+        ssk = fmaf(rows.k[tt * dkp + i], rows.k[tt * dkp + i], ssk);
+      }
+      ssq = warp_sum(ssq);
+      ssk = warp_sum(ssk);
+      const float qm = p.q_scale / sqrtf(ssq + p.unit_eps), km = 1.0f / sqrtf(ssk + p.unit_eps);
+      for (int i = lane; i < dkp; i += 32) {  // the lane's own numbers again
+        rows.q[tt * dkp + i] *= qm;
+        rows.k[tt * dkp + i] *= km;
       }
     }
   }
 }
 
-// Threads 0 .. LS_THREADS - 1 hold the state and walk; the warps behind them only fetch: while the walkers are in tile i of
-// the request's tokens, the fetchers fill the other buffer with tile i + 1, and the block meets once a tile. (A decode step
-// has one tile of one token; the walkers read their state while it is fetched.)
-template <int MODE>
+// Threads 0 .. LS_THREADS - 1 hold the state and walk; the warps behind them only fetch. Three buffers: while the walkers are in
+// tile i of the request's tokens, tile i + 1 lands and is finished and the copies of tile i + 2 are issued; the block meets once
+// a tile. (A decode step has one tile of one token; the walkers read their state while it is fetched.)
+template <int MODE, int R>
 __global__ void __launch_bounds__(LS_BLOCK, 1) linear_state_kernel(const LinearStateParams p) {
   extern __shared__ __align__(16) float sh_ls[];
   dep_launch();
   dep_wait();
-  const int seq = blockIdx.z, head = blockIdx.y, R = p.R, dk = p.dk, dv = p.dv;
+  const int seq = blockIdx.z, head = blockIdx.y, dk = p.dk, dv = p.dv;
   const int n_tok = p.seq_ntok[seq];
   if (n_tok <= 0) return;
   const int first = p.seq_qoff[seq];
-  const int dkp = R * KPT;
+  constexpr int dkp = R * KPT, a_stride = MODE == 2 ? 2 : dkp;
   const int kvh = head / (p.H / p.G);
   const bool walker = threadIdx.x < LS_THREADS;
   const int lane_r = threadIdx.x & (R - 1);
   const int col = blockIdx.x * (LS_THREADS / R) + threadIdx.x / R;
   const bool live = walker && col < dv;
-  const int a_stride = MODE == 2 ? 2 : dkp;
-  const size_t buf_floats = ((size_t)p.tile * (2 * dkp + a_stride + dv) + 3) & ~(size_t)3;  // buffers start on 16 bytes
-  auto rows_of = [&](int buf, float*& q_s, float*& k_s, float*& a_s, float*& v_s) {
-    q_s = sh_ls + (size_t)buf * buf_floats;  // [tile][dkp]
-    k_s = q_s + (size_t)p.tile * dkp;        // [tile][dkp]
-    a_s = k_s + (size_t)p.tile * dkp;        // [tile][dkp] (MODE 0/1) or [tile][2] (MODE 2)
-    v_s = a_s + (size_t)p.tile * a_stride;   // [tile][dv]
+  const int tile = p.tile, n_tiles = (n_tok + tile - 1) / tile;
+  const size_t a_floats = ((size_t)tile * a_stride + 3) & ~(size_t)3;
+  const size_t buf_floats = ((size_t)tile * (2 * dkp + dv) + a_floats + 3) & ~(size_t)3;  // every region starts on 16 bytes
+  auto rows_of = [&](int i) {
+    TileRows r;
+    r.q = sh_ls + (size_t)(i % LS_BUFFERS) * buf_floats;
+    r.k = r.q + (size_t)tile * dkp;
+    r.a = r.k + (size_t)tile * dkp;
+    r.v = r.a + a_floats;
+    return r;
   };
-  auto fetch = [&](int t0, int buf) {
-    float *q_s, *k_s, *a_s, *v_s;
-    rows_of(buf, q_s, k_s, a_s, v_s);
-    fetch_tile<MODE>(p, (size_t)(first + t0), min(p.tile, n_tok - t0), head, kvh, dk, dkp, dv, threadIdx.x - LS_THREADS,
-                     LS_BLOCK - LS_THREADS, q_s, k_s, a_s, v_s);
+  const int ftid = threadIdx.x - LS_THREADS, n_fetch = LS_BLOCK - LS_THREADS;
+  auto issue = [&](int i) {  // a group of copies a call, empty behind the last tile
+    if (i < n_tiles)
+      fetch_issue<MODE>(p, (size_t)(first + i * tile), min(tile, n_tok - i * tile), head, kvh, dk, dkp, dv, ftid, n_fetch, rows_of(i));
+    copies_commit();
+  };
+  auto finish = [&](int i) {
+    if (i < n_tiles) fetch_finish<MODE>(p, min(tile, n_tok - i * tile), dk, dkp, ftid, n_fetch, rows_of(i));
   };
 
   float* st = p.state + ((size_t)p.seq_slot[seq] * p.H + head) * (size_t)dkp * dv;
   float s[KPT], u[KPT];
+  if (walker) {
 #pragma unroll
-  for (int m = 0; m < KPT; ++m) {
-    s[m] = live ? st[((size_t)m * dv + col) * R + lane_r] : 0.f;
-    const int i = channel_of(m, lane_r, R);
-    u[m] = (MODE == 1 && i < dk) ? p.bonus[(size_t)head * dk + i] : 0.f;
-  }
-
-  if (!walker) fetch(0, 0);
-  __syncthreads();
-  for (int t0 = 0, buf = 0; t0 < n_tok; t0 += p.tile, buf ^= 1) {
-    if (walker) {
-      float *q_s, *k_s, *a_s, *v_s;
-      rows_of(buf, q_s, k_s, a_s, v_s);
-      walk_tile<MODE>(s, u, q_s, k_s, a_s, a_stride, v_s, dv, col, min(p.tile, n_tok - t0), dkp, R, lane_r, live,
-                      p.out + (size_t)(first + t0) * p.H * dv + (size_t)head * dv + col, (size_t)p.H * dv);
-    } else if (t0 + p.tile < n_tok) {
-      fetch(t0 + p.tile, buf ^ 1);
+    for (int m = 0; m < KPT; ++m) {
+      s[m] = live ? st[((size_t)m * dv + col) * R + lane_r] : 0.f;
+      const int i = channel_of(m, lane_r, R);
+      u[m] = (MODE == 1 && i < dk) ? p.bonus[(size_t)head * dk + i] : 0.f;
     }
-    __syncthreads();  // the tile has been used up, the next one is in place
+  } else {
+    issue(0);
+    issue(1);
+    copies_wait_but_last();
+    finish(0);
+  }
+  __syncthreads();
+  for (int i = 0; i < n_tiles; ++i) {
+    if (walker) {
+      const int t0 = i * tile;
+      walk_tile<MODE, R>(s, u, rows_of(i), dv, col, min(tile, n_tok - t0), lane_r, live,
+                         p.out + (size_t)(first + t0) * p.H * dv + (size_t)head * dv + col, (size_t)p.H * dv);
+    } else {
+      issue(i + 2);
+      copies_wait_but_last();
+      finish(i + 1);
+    }
+    __syncthreads();  // tile i has been used up, tile i + 1 is in place
   }
   if (live) {
 #pragma unroll
@@ -403,14 +492,32 @@ extern "C" int llm_linear_state(int mode, const float* q, int qn, long long qs, 
   p.seq_qoff = seq_qoff; p.seq_ntok = seq_ntok; p.seq_slot = seq_slot; p.out = out;
   p.H = H; p.G = G; p.dk = dk; p.dv = dv; p.R = lanes_for(dk); p.q_scale = q_scale; p.unit_eps = unit_eps;
   const int dkp = p.R * KPT;
-  auto smem_for = [&](int tile) { return 2 * (((size_t)tile * ((mode == 2 ? 2 * dkp + 2 : 3 * dkp) + dv) + 3) & ~(size_t)3) * sizeof(float); };  // two buffers
+  const int a_stride = mode == 2 ? 2 : dkp;
+  auto smem_for = [&](int tile) {  // as the kernel lays a buffer out
+    const size_t a_floats = ((size_t)tile * a_stride + 3) & ~(size_t)3;
+    return LS_BUFFERS * ((((size_t)tile * (2 * dkp + dv) + a_floats + 3) & ~(size_t)3) * sizeof(float));
+  };
   p.tile = 16;
   while (p.tile > 1 && smem_for(p.tile) > 48 * 1024) p.tile /= 2;
   LLM_REQUIRE(smem_for(p.tile) <= 48 * 1024, "linear_state: heads of %d / %d numbers exceed one block's shared memory", dk, dv);
+  p.one_part = qn == 1 && kn == 1 && vn == 1;
+  auto quads = [](const void* ptr, long long width, long long off) { return ((uintptr_t)ptr & 15) == 0 && width % 4 == 0 && off % 4 == 0; };
+  p.vec4 = dk % 4 == 0 && dv % 4 == 0 && quads(q, qw, qo) && quads(k, kw, ko) && quads(v, vw, vo) && (mode == 2 || quads(decay, decay_width, decay_off));
   dim3 grid(ceil_div(dv, LS_THREADS / p.R), H, n_seqs);
-  if (mode == 0) launch_kernel(linear_state_kernel<0>, grid, LS_BLOCK, smem_for(p.tile), stream, p);
-  else if (mode == 1) launch_kernel(linear_state_kernel<1>, grid, LS_BLOCK, smem_for(p.tile), stream, p);
-  else launch_kernel(linear_state_kernel<2>, grid, LS_BLOCK, smem_for(p.tile), stream, p);
+  const size_t smem = smem_for(p.tile);
+#define LS_LAUNCH(M, RR) launch_kernel(linear_state_kernel<M, RR>, grid, LS_BLOCK, smem, stream, p)
+#define LS_LANES(M)                  \
+  switch (p.R) {                     \
+    case 1: LS_LAUNCH(M, 1); break;  \
+    case 2: LS_LAUNCH(M, 2); break;  \
+    case 4: LS_LAUNCH(M, 4); break;  \
+    case 8: LS_LAUNCH(M, 8); break;  \
+    case 16: LS_LAUNCH(M, 16); break; \
+    default: LS_LAUNCH(M, 32); break; \
+  }
+  if (mode == 0) { LS_LANES(0) } else if (mode == 1) { LS_LANES(1) } else { LS_LANES(2) }
+#undef LS_LANES
+#undef LS_LAUNCH
   LLM_CHECK_LAUNCH("linear_state");
   return LLM_OK;
 }
