@@ -26,8 +26,9 @@
 namespace {
 
 constexpr int KPT = 16;       // state numbers of a column that one lane holds
-constexpr int LS_THREADS = 128;  // threads that hold the state
-constexpr int LS_BLOCK = 256;    // with the warps that fetch the tiles of tokens ahead
+constexpr int LS_THREADS = 128;   // threads that hold the state, at most: fewer when the blocks would not fill the device
+constexpr int LS_FETCHERS = 128;  // threads behind them that fetch the tiles of tokens ahead
+constexpr int LS_BLOCK = LS_THREADS + LS_FETCHERS;
 constexpr int LS_BUFFERS = 3;    // tiles in shared memory: walked, landing, issued
 
 __device__ __forceinline__ float parts_sum(const float* __restrict__ p, int n_parts, size_t pstride, size_t i) {
@@ -49,6 +50,7 @@ struct LinearStateParams {
   float* out;                                      // [tokens, H * dv]
   int H, G, dk, dv, R, tile;
   float q_scale, unit_eps;
+  int walkers;   // threads of a block that hold the state (a multiple of 32 and of R); LS_FETCHERS more fetch
   int one_part;  // every product comes in one part
   int vec4;      // every row and column offset is a multiple of four numbers on a 16-byte boundary
 };
@@ -314,11 +316,13 @@ __device__ __forceinline__ void fetch_finish(const LinearStateParams& p, int cnt
   }
 }
 
-// Threads 0 .. LS_THREADS - 1 hold the state and walk; the warps behind them only fetch. Three buffers: while the walkers are in
+// Threads 0 .. p.walkers - 1 hold the state and walk; the LS_FETCHERS threads behind them only fetch. Three buffers: while the walkers are in
 // tile i of the request's tokens, tile i + 1 lands and is finished and the copies of tile i + 2 are issued; the block meets once
 // a tile. (A decode step has one tile of one token; the walkers read their state while it is fetched.)
-template <int MODE, int R>
-__global__ void __launch_bounds__(LS_BLOCK, 1) linear_state_kernel(const LinearStateParams p) {
+// FEW: for steps of about a token a request (decoding). The same code held to half the registers, so that two blocks share a
+// multiprocessor: such a step is a state's trip to memory and back, and more blocks in flight hide more of it.
+template <int MODE, int R, bool FEW>
+__global__ void __launch_bounds__(LS_BLOCK, FEW ? 2 : 1) linear_state_kernel(const LinearStateParams p) {
   extern __shared__ __align__(16) float sh_ls[];
   dep_launch();
   dep_wait();
@@ -328,9 +332,9 @@ __global__ void __launch_bounds__(LS_BLOCK, 1) linear_state_kernel(const LinearS
   const int first = p.seq_qoff[seq];
   constexpr int dkp = R * KPT, a_stride = MODE == 2 ? 2 : dkp;
   const int kvh = head / (p.H / p.G);
-  const bool walker = threadIdx.x < LS_THREADS;
+  const bool walker = threadIdx.x < p.walkers;
   const int lane_r = threadIdx.x & (R - 1);
-  const int col = blockIdx.x * (LS_THREADS / R) + threadIdx.x / R;
+  const int col = blockIdx.x * (p.walkers / R) + threadIdx.x / R;
   const bool live = walker && col < dv;
   const int tile = p.tile, n_tiles = (n_tok + tile - 1) / tile;
   const size_t a_floats = ((size_t)tile * a_stride + 3) & ~(size_t)3;
@@ -343,7 +347,7 @@ __global__ void __launch_bounds__(LS_BLOCK, 1) linear_state_kernel(const LinearS
     r.v = r.a + a_floats;
     return r;
   };
-  const int ftid = threadIdx.x - LS_THREADS, n_fetch = LS_BLOCK - LS_THREADS;
+  const int ftid = threadIdx.x - p.walkers, n_fetch = LS_FETCHERS;
   auto issue = [&](int i) {  // a group of copies a call, empty behind the last tile
     if (i < n_tiles)
       fetch_issue<MODE>(p, (size_t)(first + i * tile), min(tile, n_tok - i * tile), head, kvh, dk, dkp, dv, ftid, n_fetch, rows_of(i));
@@ -459,6 +463,15 @@ __global__ void __launch_bounds__(128)
   }
 }
 
+int device_sms() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  }
+  return n;
+}
+
 int lanes_for(int dk) {
   int r = 1;
   while (r * KPT < dk) r *= 2;
@@ -476,8 +489,8 @@ extern "C" int llm_linear_state_lanes(int dk) {
 extern "C" int llm_linear_state(int mode, const float* q, int qn, long long qs, int qw, int qo, const float* k, int kn, long long ks, int kw,
                                 int ko, const float* v, int vn, long long vs, int vw, int vo, const float* decay, int decay_width,
                                 int decay_off, const float* bonus, float* state, const int* seq_qoff, const int* seq_ntok,
-                                const int* seq_slot, float* out, int n_seqs, int H, int G, int dk, int dv, float q_scale, float unit_eps,
-                                cudaStream_t stream) {
+                                const int* seq_slot, float* out, int n_tokens, int n_seqs, int H, int G, int dk, int dv, float q_scale,
+                                float unit_eps, cudaStream_t stream) {
   if (n_seqs == 0) return LLM_OK;
   LLM_REQUIRE(mode >= 0 && mode <= 2, "linear_state: unknown update rule %d", mode);
   LLM_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && H > 0 && H <= 65535 && G > 0 && H % G == 0 && dv > 0, "linear_state: bad sizes");
@@ -497,15 +510,22 @@ extern "C" int llm_linear_state(int mode, const float* q, int qn, long long qs, 
     const size_t a_floats = ((size_t)tile * a_stride + 3) & ~(size_t)3;
     return LS_BUFFERS * ((((size_t)tile * (2 * dkp + dv) + a_floats + 3) & ~(size_t)3) * sizeof(float));
   };
-  p.tile = 16;
+  const bool few = n_tokens <= 2 * n_seqs;
+  p.tile = few ? 2 : 16;
   while (p.tile > 1 && smem_for(p.tile) > 48 * 1024) p.tile /= 2;
   LLM_REQUIRE(smem_for(p.tile) <= 48 * 1024, "linear_state: heads of %d / %d numbers exceed one block's shared memory", dk, dv);
   p.one_part = qn == 1 && kn == 1 && vn == 1;
   auto quads = [](const void* ptr, long long width, long long off) { return ((uintptr_t)ptr & 15) == 0 && width % 4 == 0 && off % 4 == 0; };
   p.vec4 = dk % 4 == 0 && dv % 4 == 0 && quads(q, qw, qo) && quads(k, kw, ko) && quads(v, vw, vo) && (mode == 2 || quads(decay, decay_width, decay_off));
-  dim3 grid(ceil_div(dv, LS_THREADS / p.R), H, n_seqs);
+  // the walk is bound by what a multiprocessor's shared memory delivers a token, so few blocks are cut into more, down to a warp of walkers
+  p.walkers = LS_THREADS;
+  const long long per_column_block = (long long)H * n_seqs;
+  while (p.walkers > 32 && 2 * per_column_block * ceil_div(dv, p.walkers / p.R) <= device_sms()) p.walkers /= 2;
+  dim3 grid(ceil_div(dv, p.walkers / p.R), H, n_seqs);
   const size_t smem = smem_for(p.tile);
-#define LS_LAUNCH(M, RR) launch_kernel(linear_state_kernel<M, RR>, grid, LS_BLOCK, smem, stream, p)
+#define LS_LAUNCH(M, RR)                                                                                        \
+  if (few) launch_kernel(linear_state_kernel<M, RR, true>, grid, p.walkers + LS_FETCHERS, smem, stream, p);     \
+  else launch_kernel(linear_state_kernel<M, RR, false>, grid, p.walkers + LS_FETCHERS, smem, stream, p)
 #define LS_LANES(M)                  \
   switch (p.R) {                     \
     case 1: LS_LAUNCH(M, 1); break;  \

@@ -1326,7 +1326,7 @@ class CudaOps:
         self._check(lib.llm_linear_state(c_int(self.LINEAR_STATE_RULES[rule]), *self._sums(q, q_off, "linear_state.q"),
                                          *self._sums(k, k_off, "linear_state.k"), *self._sums(v, v_off, "linear_state.v"), _ptr(decay),
                                          c_int(decay.shape[1]), c_int(decay_off), _ptr(bonus), _ptr(state), _ptr(batch.seq_qoff),
-                                         _ptr(batch.seq_ntok), _ptr(batch.seq_slot), _ptr(out), c_int(batch.n_seqs), c_int(heads),
+                                         _ptr(batch.seq_ntok), _ptr(batch.seq_slot), _ptr(out), c_int(batch.n_tokens), c_int(batch.n_seqs), c_int(heads),
                                          c_int(kv_heads), c_int(dk), c_int(dv), c_float(q_scale), c_float(unit_eps), _stream()), lib)
         return out
 
