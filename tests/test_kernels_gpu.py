@@ -708,3 +708,74 @@ def test_kernels_refuse_what_they_cannot_take(ops):
         ops.gemm(torch.zeros(2, 2), torch.zeros(2, 2), torch.zeros(2, 2))
     with pytest.raises(KernelError):
         ops.gemm(rnd(2, 2).half(), rnd(2, 2).half(), torch.empty(2, 2, device=DEV))
+
+
+def _plain_linear_state(rule, q, k, v, decay, bonus, S, heads, kv_heads, dk, dv, q_scale, unit_eps):
+    """One request's tokens through a rule, token after token, in double precision; S [heads, dk, dv] is updated in place."""
+    n = q.shape[0]
+    out = torch.zeros(n, heads * dv, dtype=torch.float64)
+    for t in range(n):
+        for h in range(heads):
+            g = h // (heads // kv_heads)
+            qt, kt, vt = q[t, g * dk:(g + 1) * dk].clone(), k[t, g * dk:(g + 1) * dk].clone(), v[t, h * dv:(h + 1) * dv]
+            if rule == "delta":
+                if unit_eps >= 0:
+                    qt, kt = qt / torch.sqrt((qt * qt).sum() + unit_eps), kt / torch.sqrt((kt * kt).sum() + unit_eps)
+                qt = qt * q_scale
+                S[h] *= decay[t, h]
+                w = decay[t, heads + h] * (vt - S[h].T @ kt)
+                S[h] += torch.outer(kt, w)
+                o = S[h].T @ qt
+            else:
+                qt = qt * q_scale
+                a = decay[t, h * dk:(h + 1) * dk]
+                if rule == "decay_write_read":
+                    S[h] = a[:, None] * S[h] + torch.outer(kt, vt)
+                    o = S[h].T @ qt
+                else:
+                    o = (S[h] + bonus[h * dk:(h + 1) * dk, None] * torch.outer(kt, vt)).T @ qt
+                    S[h] = a[:, None] * S[h] + torch.outer(kt, vt)
+            out[t, h * dv:(h + 1) * dv] = o
+    return out
+
+
+@pytest.mark.parametrize("rule", ["decay_write_read", "bonus_read_decay_write", "delta"])
+@pytest.mark.parametrize("heads,kv_heads,dk,dv,off,parts,lengths", [
+    (2, 2, 64, 128, 0, 1, [70]),             # many tiles of one request, 16-byte copies, a grid cut into blocks of fewer walkers
+    (3, 3, 20, 10, 0, 1, [41, 1, 2]),        # part of a lane's numbers, requests of unequal length in one step
+    (2, 1, 33, 7, 3, 1, [37, 5]),            # sizes and column offsets that rule 16-byte copies out
+    (4, 2, 128, 36, 4, 3, [1, 1, 1]),        # products in several parts, a token a request
+    (2, 2, 130, 24, 8, 2, [19, 2]),          # more than eight lanes a column, parts and a portion together
+])
+def test_linear_state_rules_alone(ops, rule, heads, kv_heads, dk, dv, off, parts, lengths):
+    """Each update rule of the linear-state kernel against a plain loop: every way the tokens' rows reach shared memory, states
+    handed on through slots between two steps, slots in another order than the requests."""
+    import types
+    if rule != "delta":
+        kv_heads = heads
+    g = torch.Generator().manual_seed(dk * 7 + dv)
+    n_seqs, slots = len(lengths), [3, 0, 2][:len(lengths)]
+    state = torch.zeros((4,) + tuple(ops.linear_state_shape(heads, dk, dv)), dtype=torch.float32, device=DEV)
+    S = [torch.zeros(heads, dk, dv, dtype=torch.float64) for _ in lengths]
+    bonus = torch.randn(heads * dk, generator=g) if rule == "bonus_read_decay_write" else None
+    q_scale, unit_eps = dk ** -0.5, (1e-6 if rule == "delta" else -1.0)
+    for step in range(2):
+        n = sum(lengths)
+        wq, wv, wd = off + kv_heads * dk + 4, off + heads * dv, off + (2 * heads if rule == "delta" else heads * dk)
+
+        def sums(width):  # float32 sums in `parts` parts and their total in double precision
+            t = torch.randn(parts, n, width, generator=g)
+            return (t if parts > 1 else t[0]).contiguous().to(DEV), t.double().sum(0)
+        (q, qd), (k, kd), (v, vd) = sums(wq), sums(wq), sums(wv)
+        decay = torch.rand(n, wd, generator=g) * 0.3 + 0.7
+        qoff = [sum(lengths[:i]) for i in range(n_seqs)]
+        batch = types.SimpleNamespace(seq_qoff=torch.tensor(qoff, dtype=torch.int32, device=DEV), seq_ntok=torch.tensor(lengths, dtype=torch.int32, device=DEV),
+                                      seq_slot=torch.tensor(slots, dtype=torch.int32, device=DEV), n_seqs=n_seqs, n_tokens=n)
+        out = torch.full((n, heads * dv), float("nan"), dtype=torch.float32, device=DEV)
+        ops.linear_state(rule, q, off, k, off, v, off, decay.to(DEV), off, None if bonus is None else bonus.to(DEV), state, batch, out, heads,
+                         kv_heads, dk, dv, q_scale, unit_eps)
+        for i, (o, l) in enumerate(zip(qoff, lengths)):
+            want = _plain_linear_state(rule, qd[o:o + l, off:], kd[o:o + l, off:], vd[o:o + l, off:], decay[o:o + l, off:].double(),
+                                       None if bonus is None else bonus.double(), S[i], heads, kv_heads, dk, dv, q_scale, unit_eps)
+            torch.testing.assert_close(out[o:o + l].double().cpu(), want, atol=2e-4, rtol=2e-4, msg=lambda m: f"step {step} request {i}: {m}")
+    assert float(state[1].abs().max()) == 0.0, "a slot that no request named was written"
