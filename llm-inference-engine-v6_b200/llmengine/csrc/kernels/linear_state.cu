@@ -9,9 +9,9 @@
 // Every column S[:, j] evolves by itself, so a block takes a (request, head, tile of columns) and walks the request's tokens of the
 // step in order; a column's dk numbers are spread over R lanes of a warp (KPT = 16 numbers a lane), the two dot products of a
 // token are sums over a lane's numbers and then over the R lanes (xor shuffles, a fixed order). The tokens' q, k, decays and v
-// come through shared memory in tiles of a few tokens (a warp a token: the sums of the products' parts, the unit norms and the
-// query's scale are applied there), so the walk itself only syncs once a tile. Results never depend on how a request was cut into
-// steps, on the batch or on the slot: the same additions happen in the same order.
+// come through shared memory in tiles of a few tokens that warps of their own fetch ahead of the walk (the sums of the products'
+// parts, the unit norms and the query's scale are applied there), so the walk itself only syncs once a tile. Results never depend
+// on how a request was cut into steps, on the batch or on the slot: the same additions happen in the same order.
 //
 // In the slot a head's matrix is stored as the threads hold it: number (m, column j, lane r) at ((m * dv + j) * R + r), which is
 // S[channel_of(m, r, R), j]; loads and stores of a warp are then 128 contiguous bytes. R = the power of two >= dk / 16.
@@ -105,7 +105,7 @@ __device__ __forceinline__ void walk_tile(float (&s)[KPT], const float (&u)[KPT]
   };
   read(0, kk, qq, aa, vj, g, beta);
   float pend = 0.f;
-#pragma unroll 2
+#pragma unroll 4
   for (int tt = 0; tt < cnt; ++tt) {
     float kn[KPT], qn[KPT], an[KPT], vn, gn = 0.f, bn = 0.f;
     read(min(tt + 1, cnt - 1), kn, qn, an, vn, gn, bn);
