@@ -80,6 +80,23 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   return red[32];
 }
 
+// What a gated feed-forward applies to a (gate, up) pair of sums.
+// act 0: silu, g / (1 + exp(-g)); act 1: the tanh form of gelu, 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3)))
+// act 2: both sides limited, a sigmoid of slope p1 on the gate, the up side raised by one:
+//        g <- min(g, p0), u <- clamp(u, -p0, p0), result g * sigmoid(p1 * g) * (u + 1)
+__device__ __forceinline__ float gate_activation(float g, int act) {
+  if (act == 1) return 0.5f * g * (1.0f + tanhf(0.79788456080286535588f * (g + 0.044715f * g * g * g)));
+  return g / (1.0f + expf(-g));
+}
+__device__ __forceinline__ float gated_value(float g, float u, int act, float p0, float p1) {
+  if (act == 2) {
+    g = fminf(g, p0);
+    u = fminf(fmaxf(u, -p0), p0);
+    return g / (1.0f + expf(-p1 * g)) * (u + 1.0f);
+  }
+  return gate_activation(g, act) * u;
+}
+
 static inline int ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
 
 // ---------------------------------------------------------------------------------------------

@@ -57,7 +57,9 @@ extern "C" int llm_embed(const void* table, int table_dtype, const int* ids, flo
 // ------------------------------------------------------------------------------------ RMSNorm
 // One block per output row. Source row r = rows ? rows[blockIdx.x] : blockIdx.x.
 // x = h[r] + sum_p delta[p][r] (partials added in index order); if write_back, h[r] = x.
-// out[blockIdx.x] = (w * x) * inv_rms.
+// out[blockIdx.x] = (w * x) * inv_rms. With `center` (a layer norm without bias) the row's mean is taken off first:
+// out = w * (x - mean) / sqrt(mean((x - mean)^2) + eps), the variance from the deviations themselves (two passes over
+// the row in registers), never from sum(x^2) - mean^2.
 template <typename T>
 __device__ __forceinline__ void store4(T* dst, float a, float b, float c, float d);
 template <>
@@ -78,7 +80,7 @@ template <typename TOut, int R>
 __global__ void __launch_bounds__(1024) rmsnorm_vec_kernel(float* __restrict__ h, const float* __restrict__ delta, int n_partials,
                                                            size_t partial_stride, const float* __restrict__ w,
                                                            const int* __restrict__ rows, TOut* __restrict__ out, int dim,
-                                                           float eps, int write_back) {
+                                                           float eps, int write_back, int center) {
   __shared__ float red[33];
   dep_launch();
   float4 wv[R];
@@ -136,6 +138,21 @@ __global__ void __launch_bounds__(1024) rmsnorm_vec_kernel(float* __restrict__ h
       ss += x[k].x * x[k].x + x[k].y * x[k].y + x[k].z * x[k].z + x[k].w * x[k].w;
     }
   }
+  if (center) {
+    float sm = 0.f;
+#pragma unroll
+    for (int k = 0; k < R; ++k) sm += (x[k].x + x[k].y) + (x[k].z + x[k].w);  // lanes beyond the row hold zeros
+    const float mean = block_sum(sm, red) / (float)dim;
+    ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < R; ++k) {
+      const int i = (threadIdx.x + k * blockDim.x) * 4;
+      if (i < dim) {
+        x[k].x -= mean; x[k].y -= mean; x[k].z -= mean; x[k].w -= mean;
+        ss += x[k].x * x[k].x + x[k].y * x[k].y + x[k].z * x[k].z + x[k].w * x[k].w;
+      }
+    }
+  }
   ss = block_sum(ss, red);
   const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
   TOut* o = out + (size_t)blockIdx.x * dim;
@@ -151,14 +168,14 @@ template <typename TOut>
 __global__ void rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta, int n_partials,
                                size_t partial_stride, const float* __restrict__ w,
                                const int* __restrict__ rows, TOut* __restrict__ out, int dim, float eps,
-                               int write_back) {
+                               int write_back, int center) {
   __shared__ float red[33];
   dep_launch();
   dep_wait();
   const int r = rows ? rows[blockIdx.x] : blockIdx.x;
   float* hr = h + (size_t)r * dim;
   const float* dr = delta ? delta + (size_t)r * dim : nullptr;
-  float ss = 0.f;
+  float ss = 0.f, sm = 0.f;
   for (int i = threadIdx.x; i < dim; i += blockDim.x) {
     float x = hr[i];
     if (dr) {
@@ -166,21 +183,34 @@ __global__ void rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ 
       if (write_back) hr[i] = x;
     }
     ss += x * x;
+    sm += x;
+  }
+  const bool again = dr && !write_back;  // the sum was not kept: it is formed again, the same additions in the same order
+  float mean = 0.f;
+  if (center) {
+    mean = block_sum(sm, red) / (float)dim;
+    ss = 0.f;
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+      float x = hr[i];
+      if (again)
+        for (int p = 0; p < n_partials; ++p) x += dr[(size_t)p * partial_stride + i];
+      ss += (x - mean) * (x - mean);
+    }
   }
   ss = block_sum(ss, red);
   const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
   TOut* o = out + (size_t)blockIdx.x * dim;
   for (int i = threadIdx.x; i < dim; i += blockDim.x) {
     float x = hr[i];
-    if (dr && !write_back)
+    if (again)
       for (int p = 0; p < n_partials; ++p) x += dr[(size_t)p * partial_stride + i];
-    o[i] = from_f32<TOut>((w[i] * x) * inv);
+    o[i] = from_f32<TOut>((w[i] * (x - mean)) * inv);
   }
 }
 
 template <typename TOut>
 static void launch_rmsnorm(float* h, const float* delta, int n_partials, size_t partial_stride, const float* w, const int* rows,
-                           TOut* out, int n_out_rows, int dim, float eps, int write_back, cudaStream_t stream) {
+                           TOut* out, int n_out_rows, int dim, float eps, int write_back, int center, cudaStream_t stream) {
   auto al = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; };
   const bool vec = dim % 4 == 0 && dim <= 16384 && al(h) && al(w) && al(out) && (!delta || (al(delta) && partial_stride % 4 == 0));
   if (vec) {
@@ -191,29 +221,29 @@ static void launch_rmsnorm(float* h, const float* delta, int n_partials, size_t 
     if (n_out_rows >= 512 && quads >= 256 && quads <= 4096) threads = ((quads / 4 + 31) / 32) * 32;
     const int per_thread = (quads + threads - 1) / threads;
     if (per_thread == 1)
-      launch_kernel(rmsnorm_vec_kernel<TOut, 1>, n_out_rows, threads, 0, stream, h, delta, n_partials, partial_stride, w, rows, out, dim, eps, write_back);
+      launch_kernel(rmsnorm_vec_kernel<TOut, 1>, n_out_rows, threads, 0, stream, h, delta, n_partials, partial_stride, w, rows, out, dim, eps, write_back, center);
     else if (per_thread == 2)
-      launch_kernel(rmsnorm_vec_kernel<TOut, 2>, n_out_rows, threads, 0, stream, h, delta, n_partials, partial_stride, w, rows, out, dim, eps, write_back);
+      launch_kernel(rmsnorm_vec_kernel<TOut, 2>, n_out_rows, threads, 0, stream, h, delta, n_partials, partial_stride, w, rows, out, dim, eps, write_back, center);
     else
-      launch_kernel(rmsnorm_vec_kernel<TOut, 4>, n_out_rows, threads, 0, stream, h, delta, n_partials, partial_stride, w, rows, out, dim, eps, write_back);
+      launch_kernel(rmsnorm_vec_kernel<TOut, 4>, n_out_rows, threads, 0, stream, h, delta, n_partials, partial_stride, w, rows, out, dim, eps, write_back, center);
     return;
   }
   int threads = 128;
   while (threads < 1024 && threads * 4 < dim) threads *= 2;
-  launch_kernel(rmsnorm_kernel<TOut>, n_out_rows, threads, 0, stream, h, delta, n_partials, partial_stride, w, rows, out, dim, eps, write_back);
+  launch_kernel(rmsnorm_kernel<TOut>, n_out_rows, threads, 0, stream, h, delta, n_partials, partial_stride, w, rows, out, dim, eps, write_back, center);
 }
 
 extern "C" int llm_rmsnorm(float* h, const float* delta, int n_partials, long long partial_stride,
                            const float* w, const int* rows, void* out, int out_dtype, int n_out_rows,
-                           int dim, float eps, int write_back, cudaStream_t stream) {
+                           int dim, float eps, int write_back, int center, cudaStream_t stream) {
   if (n_out_rows == 0) return LLM_OK;
   LLM_REQUIRE(n_out_rows > 0 && dim > 0, "rmsnorm: bad sizes rows=%d dim=%d", n_out_rows, dim);
   LLM_REQUIRE(!(rows && write_back), "rmsnorm: write_back with a row list is not allowed");
   LLM_REQUIRE(!delta || n_partials >= 1, "rmsnorm: delta needs n_partials >= 1");
   if (out_dtype == LLM_F32)
-    launch_rmsnorm<float>(h, delta, n_partials, (size_t)partial_stride, w, rows, (float*)out, n_out_rows, dim, eps, write_back, stream);
+    launch_rmsnorm<float>(h, delta, n_partials, (size_t)partial_stride, w, rows, (float*)out, n_out_rows, dim, eps, write_back, center, stream);
   else if (out_dtype == LLM_BF16)
-    launch_rmsnorm<bf16>(h, delta, n_partials, (size_t)partial_stride, w, rows, (bf16*)out, n_out_rows, dim, eps, write_back, stream);
+    launch_rmsnorm<bf16>(h, delta, n_partials, (size_t)partial_stride, w, rows, (bf16*)out, n_out_rows, dim, eps, write_back, center, stream);
   else
     LLM_REQUIRE(false, "rmsnorm: unknown out dtype %d", out_dtype);
   LLM_CHECK_LAUNCH("rmsnorm");
@@ -252,22 +282,6 @@ __device__ __forceinline__ void gate_up_columns(int c, int ff, int block, size_t
     *gate = (size_t)(c / block) * 2 * block + (c % block);
     *up = *gate + block;
   }
-}
-
-// act 0: silu, g / (1 + exp(-g)); act 1: the tanh form of gelu, 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3)))
-// act 2: both sides limited, a sigmoid of slope p1 on the gate, the up side raised by one:
-//        g <- min(g, p0), u <- clamp(u, -p0, p0), result g * sigmoid(p1 * g) * (u + 1)
-__device__ __forceinline__ float gate_activation(float g, int act) {
-  if (act == 1) return 0.5f * g * (1.0f + tanhf(0.79788456080286535588f * (g + 0.044715f * g * g * g)));
-  return g / (1.0f + expf(-g));
-}
-__device__ __forceinline__ float gated_value(float g, float u, int act, float p0, float p1) {
-  if (act == 2) {
-    g = fminf(g, p0);
-    u = fminf(fmaxf(u, -p0), p0);
-    return g / (1.0f + expf(-p1 * g)) * (u + 1.0f);
-  }
-  return gate_activation(g, act) * u;
 }
 
 template <typename T>
@@ -683,5 +697,22 @@ extern "C" int llm_pair_combine(const float* a, int na, long long sa, const floa
   LLM_REQUIRE(n_rows > 0 && dim > 0 && a && b && na >= 1 && nb >= 1 && out, "pair_combine: bad arguments");
   launch_kernel(pair_combine_kernel, n_rows, 256, 0, stream, a, na, (size_t)sa, b, nb, (size_t)sb, wa, wb, ca, cb, eps, out, dim);
   LLM_CHECK_LAUNCH("pair_combine");
+  return LLM_OK;
+}
+
+// ------------------------------------------------------------------------------------ capped logits
+// x <- cap * tanh(x / cap), float32 in place: logits squeezed smoothly into (-cap, cap) before anything reads them.
+__global__ void softcap_kernel(float* __restrict__ x, size_t total, float cap, float inv_cap) {
+  dep_launch();
+  dep_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < total) x[i] = cap * tanhf(x[i] * inv_cap);
+}
+
+extern "C" int llm_softcap(float* x, long long total, float cap, cudaStream_t stream) {
+  if (total == 0) return LLM_OK;
+  LLM_REQUIRE(total > 0 && cap > 0.f, "softcap: needs a positive cap");
+  launch_kernel(softcap_kernel, ceil_div(total, 256), 256, 0, stream, x, (size_t)total, cap, 1.0f / cap);
+  LLM_CHECK_LAUNCH("softcap");
   return LLM_OK;
 }

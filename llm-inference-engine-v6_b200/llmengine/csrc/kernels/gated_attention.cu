@@ -2,7 +2,8 @@
 // precisions, any sizes):
 //
 //   qkv_prep   per token, from the float32 sums of the [Wq; Wk; Wv; Wg] product: RMS norm of every query and key head over its
-//              dk numbers with one weight for all heads (optional), rotation of the first rot_dims numbers of a head in the
+//              dk numbers with one weight for all heads (optional; or, `norm_wide`, one RMS norm over all query heads' numbers at
+//              once and one over all key heads', with a weight a number), rotation of the first rot_dims numbers of a head in the
 //              half-split layout from (cos, sin) tables, value mixing v <- (1 - lambda) v + lambda v_first with the values that
 //              an earlier layer of the same step left for these tokens (or leaving them), and the write of k and v into the
 //              token's page. Keys have dk numbers a head, values dv.
@@ -35,8 +36,10 @@ __global__ void __launch_bounds__(PREP_WARPS * 32)
                     const float* __restrict__ wq, const float* __restrict__ wk, float eps, const float* __restrict__ cos_t,
                     const float* __restrict__ sin_t, const int* __restrict__ positions, const int* __restrict__ token_seq,
                     const int* __restrict__ block_table, int max_blocks, T* __restrict__ q_out, long long ld_q, T* __restrict__ kcache,
-                    T* __restrict__ vcache, int page_size, int mix_role, const float* __restrict__ lambda, float* __restrict__ v_first) {
+                    T* __restrict__ vcache, int page_size, int mix_role, const float* __restrict__ lambda, float* __restrict__ v_first,
+                    int norm_wide) {
   extern __shared__ float sh[];  // PREP_WARPS rows of dk
+  __shared__ float red[33];
   dep_launch();
   dep_wait();
   const int tok = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -48,11 +51,33 @@ __global__ void __launch_bounds__(PREP_WARPS * 32)
   const int page = block_table[(size_t)token_seq[tok] * max_blocks + pos / page_size];
   const int in_page = pos % page_size;
   float* buf = sh + (size_t)warp * dk;
+  // norm_wide: the norm's statistic is over the whole projection, so every block of the token forms both sums of squares
+  // first (the block's threads in turn, then block_sum: an order that depends on the sizes alone)
+  float inv_q = 1.f, inv_k = 1.f;
+  if (norm_wide) {
+    if (wq) {
+      float ss = 0.f;
+      for (int i = threadIdx.x; i < H * dk; i += blockDim.x) {
+        const float v = parts_sum(parts, n_parts, pstride, row + i);
+        ss += v * v;
+      }
+      inv_q = 1.0f / sqrtf(block_sum(ss, red) / (float)(H * dk) + eps);
+    }
+    if (wk && G > 0) {
+      float ss = 0.f;
+      for (int i = threadIdx.x; i < G * dk; i += blockDim.x) {
+        const float v = parts_sum(parts, n_parts, pstride, row + (size_t)H * dk + i);
+        ss += v * v;
+      }
+      inv_k = 1.0f / sqrtf(block_sum(ss, red) / (float)(G * dk) + eps);
+    }
+  }
   // query heads 0..H-1, then key heads H..H+G-1: a warp a head; the blocks of a token (blockIdx.y) share its heads and values
   for (int head = blockIdx.y * PREP_WARPS + warp; head < H + G; head += gridDim.y * PREP_WARPS) {
     const bool is_q = head < H;
     const size_t col0 = is_q ? (size_t)head * dk : (size_t)H * dk + (size_t)(head - H) * dk;
     const float* w = is_q ? wq : wk;
+    if (w && norm_wide) w += (size_t)(is_q ? head : head - H) * dk;  // a weight a number of the projection
     float ss = 0.f;
     for (int d = lane; d < dk; d += 32) {
       const float v = parts_sum(parts, n_parts, pstride, row + col0 + d);
@@ -60,7 +85,7 @@ __global__ void __launch_bounds__(PREP_WARPS * 32)
       ss += v * v;
     }
     ss = warp_sum(ss);
-    const float inv = w ? 1.0f / sqrtf(ss / (float)dk + eps) : 1.0f;
+    const float inv = !w ? 1.0f : norm_wide ? (is_q ? inv_q : inv_k) : 1.0f / sqrtf(ss / (float)dk + eps);
     __syncwarp();
     for (int d = lane; d < dk; d += 32) buf[d] = w ? buf[d] * inv * w[d] : buf[d];
     __syncwarp();
@@ -187,9 +212,12 @@ extern "C" int llm_qkv_prep(const float* parts, int n_parts, long long pstride, 
                             const float* wq, const float* wk, float eps, const float* cos_t, const float* sin_t, const int* positions,
                             const int* token_seq, const int* block_table, int max_blocks, void* q_out, long long ld_q, void* kcache,
                             void* vcache, int page_size, int mix_role, const float* lambda, float* v_first, int dtype, int n_tokens,
-                            cudaStream_t stream) {
+                            int norm_wide, cudaStream_t stream) {
+  // G 0: the product holds queries alone (a layer that reads another layer's keys and values): nothing is written to a cache.
+  // norm_wide: wq [H * dk] and wk [G * dk], one RMS norm over each whole projection instead of one a head
   if (n_tokens == 0) return LLM_OK;
-  LLM_REQUIRE(n_tokens > 0 && n_parts >= 1 && H > 0 && G > 0 && dk > 0 && dv > 0, "qkv_prep: bad sizes");
+  LLM_REQUIRE(n_tokens > 0 && n_parts >= 1 && H > 0 && G >= 0 && dk > 0 && dv > 0, "qkv_prep: bad sizes");
+  LLM_REQUIRE(G > 0 || (kcache == nullptr && mix_role == 0), "qkv_prep: a product without keys and values writes none");
   LLM_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dk, "qkv_prep: %d rotated dimensions do not fit a head of %d", rot_dims, dk);
   LLM_REQUIRE(rot_dims == 0 || (cos_t && sin_t), "qkv_prep: rotation tables missing");
   LLM_REQUIRE((size_t)(H + G) * dk + (size_t)G * dv <= (size_t)width, "qkv_prep: columns outside the product");
@@ -202,7 +230,7 @@ extern "C" int llm_qkv_prep(const float* parts, int n_parts, long long pstride, 
 #define LLM_PREP(T)                                                                                                                  \
   launch_kernel(qkv_prep_kernel<T>, grid, PREP_WARPS * 32, smem, stream, parts, n_parts, (size_t)pstride, width, H, G, dk, dv,    \
                 rot_dims, wq, wk, eps, cos_t, sin_t, positions, token_seq, block_table, max_blocks, (T*)q_out, ld_q, (T*)kcache,       \
-                (T*)vcache, page_size, mix_role, lambda, v_first)
+                (T*)vcache, page_size, mix_role, lambda, v_first, norm_wide)
   if (dtype == LLM_F32) LLM_PREP(float);
   else if (dtype == LLM_BF16) LLM_PREP(bf16);
   else LLM_REQUIRE(false, "qkv_prep: unknown dtype %d", dtype);

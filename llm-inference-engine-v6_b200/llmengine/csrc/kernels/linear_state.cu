@@ -472,6 +472,30 @@ int device_sms() {
   return n;
 }
 
+// Rotation of float32 sums for mixers whose recurrence reads rotated queries and keys: for every token and each of `heads` heads
+// of dk numbers that lie side by side from column `off` of the sums, the pair (i, i + rot_dims / 2) of the head's first rot_dims
+// numbers turns by the token's position (cos / sin tables [positions, rot_dims / 2]); heads from `scaled_from` on are then
+// multiplied by `scale`. out [tokens, heads * dk] float32: nothing is rounded on the way.
+__global__ void rotate_sums_kernel(Sums x, int heads, int dk, int rot_dims, const float* __restrict__ cos_t, const float* __restrict__ sin_t,
+                                   const int* __restrict__ positions, float* __restrict__ out, int n_tokens, int scaled_from, float scale) {
+  dep_launch();
+  dep_wait();
+  const int per = heads * dk;
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)n_tokens * per) return;
+  const int tok = (int)(i / per), c = (int)(i - (size_t)tok * per), head = c / dk, d = c - head * dk, half = rot_dims / 2;
+  const size_t at = (size_t)tok * x.width + x.off + c;
+  float v = parts_sum(x.p, x.n, x.stride, at);
+  if (d < rot_dims) {
+    const int pr = d < half ? d : d - half;
+    const float cs = cos_t[(size_t)positions[tok] * half + pr], sn = sin_t[(size_t)positions[tok] * half + pr];
+    const float other = parts_sum(x.p, x.n, x.stride, d < half ? at + half : at - half);
+    v = d < half ? v * cs - other * sn : v * cs + other * sn;
+  }
+  out[i] = head >= scaled_from ? v * scale : v;
+}
+
+
 int lanes_for(int dk) {
   int r = 1;
   while (r * KPT < dk) r *= 2;
@@ -490,7 +514,8 @@ extern "C" int llm_linear_state(int mode, const float* q, int qn, long long qs, 
                                 int ko, const float* v, int vn, long long vs, int vw, int vo, const float* decay, int decay_width,
                                 int decay_off, const float* bonus, float* state, const int* seq_qoff, const int* seq_ntok,
                                 const int* seq_slot, float* out, int n_tokens, int n_seqs, int H, int G, int dk, int dv, float q_scale,
-                                float unit_eps, cudaStream_t stream) {
+                                float unit_eps, int decay_const, cudaStream_t stream) {
+  // decay_const: `decay` is one row that holds for every token (decays that are constants of the model)
   if (n_seqs == 0) return LLM_OK;
   LLM_REQUIRE(mode >= 0 && mode <= 2, "linear_state: unknown update rule %d", mode);
   LLM_REQUIRE(n_seqs > 0 && n_seqs <= 65535 && H > 0 && H <= 65535 && G > 0 && H % G == 0 && dv > 0, "linear_state: bad sizes");
@@ -501,7 +526,7 @@ extern "C" int llm_linear_state(int mode, const float* q, int qn, long long qs, 
               "linear_state: columns outside their rows");
   LinearStateParams p;
   p.q = Sums{q, qn, (size_t)qs, qw, qo}; p.k = Sums{k, kn, (size_t)ks, kw, ko}; p.v = Sums{v, vn, (size_t)vs, vw, vo};
-  p.decay = decay; p.decay_width = decay_width; p.decay_off = decay_off; p.bonus = bonus; p.state = state;
+  p.decay = decay; p.decay_width = decay_const ? 0 : decay_width; p.decay_off = decay_off; p.bonus = bonus; p.state = state;
   p.seq_qoff = seq_qoff; p.seq_ntok = seq_ntok; p.seq_slot = seq_slot; p.out = out;
   p.H = H; p.G = G; p.dk = dk; p.dv = dv; p.R = lanes_for(dk); p.q_scale = q_scale; p.unit_eps = unit_eps;
   const int dkp = p.R * KPT;
@@ -516,7 +541,7 @@ extern "C" int llm_linear_state(int mode, const float* q, int qn, long long qs, 
   LLM_REQUIRE(smem_for(p.tile) <= 48 * 1024, "linear_state: heads of %d / %d numbers exceed one block's shared memory", dk, dv);
   p.one_part = qn == 1 && kn == 1 && vn == 1;
   auto quads = [](const void* ptr, long long width, long long off) { return ((uintptr_t)ptr & 15) == 0 && width % 4 == 0 && off % 4 == 0; };
-  p.vec4 = dk % 4 == 0 && dv % 4 == 0 && quads(q, qw, qo) && quads(k, kw, ko) && quads(v, vw, vo) && (mode == 2 || quads(decay, decay_width, decay_off));
+  p.vec4 = dk % 4 == 0 && dv % 4 == 0 && quads(q, qw, qo) && quads(k, kw, ko) && quads(v, vw, vo) && (mode == 2 || quads(decay, p.decay_width, decay_off));
   // the walk is bound by what a multiprocessor's shared memory delivers a token, so few blocks are cut into more, down to a warp of walkers
   p.walkers = LS_THREADS;
   const long long per_column_block = (long long)H * n_seqs;
@@ -588,5 +613,17 @@ extern "C" int llm_head_norm_gate(const float* o, const float* weight, int weigh
   else
     LLM_REQUIRE(false, "head_norm_gate: unknown dtype %d", dtype);
   LLM_CHECK_LAUNCH("head_norm_gate");
+  return LLM_OK;
+}
+
+extern "C" int llm_rotate_sums(const float* x, int xn, long long xs, int xw, int xo, int heads, int dk, int rot_dims, const float* cos_t,
+                               const float* sin_t, const int* positions, float* out, int n_tokens, int scaled_from, float scale,
+                               cudaStream_t stream) {
+  if (n_tokens == 0) return LLM_OK;
+  LLM_REQUIRE(n_tokens > 0 && heads > 0 && dk > 0 && x && out && xn >= 1 && xo >= 0 && (long long)xo + (long long)heads * dk <= xw, "rotate_sums: bad arguments");
+  LLM_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dk && (rot_dims == 0 || (cos_t && sin_t && positions)), "rotate_sums: %d rotated numbers in a head of %d", rot_dims, dk);
+  launch_kernel(rotate_sums_kernel, ceil_div((long long)n_tokens * heads * dk, 256), 256, 0, stream, Sums{x, xn, (size_t)xs, xw, xo}, heads, dk,
+                rot_dims, cos_t, sin_t, positions, out, n_tokens, scaled_from, scale);
+  LLM_CHECK_LAUNCH("rotate_sums");
   return LLM_OK;
 }

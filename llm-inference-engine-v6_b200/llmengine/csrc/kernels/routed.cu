@@ -85,17 +85,19 @@ __global__ void route_kernel(const T* __restrict__ x, long long ldx, const T* __
 template <typename T>
 __global__ void route_grouped_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__ wr, const float* __restrict__ correction,
                                      int D, int E, int top, int n_groups, int keep, float norm_eps, int* __restrict__ idx,
-                                     float* __restrict__ share, int score_mode, int group_top, int normalize) {
-  extern __shared__ float sh_r[];  // s[E], choice[E], group score[n_groups]
+                                     float* __restrict__ share, int score_mode, int group_top, int normalize, float weight_scale,
+                                     float* __restrict__ gate_out) {
+  extern __shared__ float sh_r[];  // s[E + 1], choice[E], group score[n_groups]
   float* s = sh_r;
-  float* choice = sh_r + E;
-  float* gscore = sh_r + 2 * E;
+  float* choice = sh_r + E + 1;
+  float* gscore = sh_r + 2 * E + 1;
   dep_launch();
   dep_wait();
   const int tok = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
   const T* xr = x + (size_t)tok * ldx;
   const bool vec = D % 8 == 0 && sizeof(T) == 2 && (reinterpret_cast<uintptr_t>(xr) & 15u) == 0 && (reinterpret_cast<uintptr_t>(wr) & 15u) == 0;
-  for (int e = warp; e < E; e += nw) {
+  const int n_rows = E + (gate_out ? 1 : 0);  // with gate_out, one more row behind the router's: a gate's logit, no expert
+  for (int e = warp; e < n_rows; e += nw) {
     const T* w = wr + (size_t)e * D;
     float acc = 0.f;
     if (vec) {  // bfloat16 rows, 16 bytes a lane a step
@@ -118,6 +120,7 @@ __global__ void route_grouped_kernel(const T* __restrict__ x, long long ldx, con
   }
   __syncthreads();
   if (warp != 0) return;
+  if (gate_out && lane == 0) gate_out[tok] = 1.0f / (1.0f + expf(-s[E]));
   if (score_mode == 1) {  // every expert's score by itself: sigmoid of its logit
     for (int e = lane; e < E; e += 32) {
       const float p = 1.0f / (1.0f + expf(-s[e]));
@@ -190,12 +193,18 @@ __global__ void route_grouped_kernel(const T* __restrict__ x, long long ldx, con
     }
     __syncwarp();
   }
-  if (normalize && lane < top) share[(size_t)tok * top + lane] /= (total + norm_eps);
+  __syncwarp();
+  if (lane < top) {
+    float p = share[(size_t)tok * top + lane];
+    if (normalize) p /= (total + norm_eps);
+    share[(size_t)tok * top + lane] = p * weight_scale;  // a scale of 1 changes nothing
+  }
 }
 
 // One block. counts -> tiles per expert -> scatter. The order of an expert's rows depends on timing;
 // every row's result is computed on its own, so nothing depends on that order.
-__global__ void group_kernel(const int* __restrict__ idx, int n_pairs, int E, int tile, int max_tiles, int* __restrict__ tile_expert,
+// Experts from `real` on have no matrices (their pairs are dealt with where the results are added): they get no tiles.
+__global__ void group_kernel(const int* __restrict__ idx, int n_pairs, int E, int real, int tile, int max_tiles, int* __restrict__ tile_expert,
                              int* __restrict__ tile_rows) {
   extern __shared__ int sh[];  // counts[E], start[E] (in rows, tile-aligned), cursor[E]
   int* counts = sh;
@@ -212,8 +221,8 @@ __global__ void group_kernel(const int* __restrict__ idx, int n_pairs, int E, in
   if (threadIdx.x == 0) {
     int at = 0;
     for (int e = 0; e < E; ++e) {
-      start[e] = at * tile;
-      const int nt = (counts[e] + tile - 1) / tile;
+      start[e] = e < real ? at * tile : -1;
+      const int nt = e < real ? (counts[e] + tile - 1) / tile : 0;
       for (int k = 0; k < nt; ++k) tile_expert[at + k] = e;
       at += nt;
     }
@@ -221,19 +230,19 @@ __global__ void group_kernel(const int* __restrict__ idx, int n_pairs, int E, in
   __syncthreads();
   for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
     const int e = idx[i];
-    tile_rows[start[e] + atomicAdd(&cursor[e], 1)] = i;
+    if (start[e] >= 0) tile_rows[start[e] + atomicAdd(&cursor[e], 1)] = i;
   }
 }
 
 constexpr int RP_WARPS = 4, RP_ROWS = 8;  // rows of a tile of the CUDA-core product
 
 // epilogue 0: exact gelu; 1: times share[pair]; 2: w holds 2 N rows, row 2 n a gate and row 2 n + 1 its up row:
-// out[p, n] = silu(gate) * up
+// out[p, n] = gated_value(gate, up) with the activation (act, p0, p1) of common.cuh: silu(gate) * up, or both sides limited
 template <typename TA, typename TO>
 __global__ void __launch_bounds__(RP_WARPS * 32)
     routed_product_kernel(const TA* __restrict__ a, long long lda, int a_div, const TA* __restrict__ w, long long w_stride, int N, int K,
                           const int* __restrict__ tile_expert, const int* __restrict__ tile_rows, TO* __restrict__ out, long long ldo,
-                          int epilogue, const float* __restrict__ share) {
+                          int epilogue, const float* __restrict__ share, int act, float p0, float p1) {
   dep_launch();
   dep_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -266,7 +275,7 @@ __global__ void __launch_bounds__(RP_WARPS * 32)
 #pragma unroll
     for (int i = 0; i < RP_ROWS; ++i) {
       const float g = warp_sum(acc[i]), u = warp_sum(acc2[i]);
-      acc[i] = g / (1.0f + expf(-g)) * u;
+      acc[i] = gated_value(g, u, act, p0, p1);
     }
   } else {
     for (int k = lane; k < K; k += 32) {
@@ -292,7 +301,13 @@ __global__ void __launch_bounds__(RP_WARPS * 32)
   }
 }
 
-__global__ void combine_kernel(const float* __restrict__ y, float* __restrict__ out, int top, int D, size_t total) {
+// idx (with x, share, real): a choice of an expert from `real` on is an identity expert, whose result is the token's own
+// input row times the choice's weight. b (with gate): float32 partial sums of an expert that every token uses, added after
+// the chosen ones, times gate[token].
+template <typename T>
+__global__ void combine_kernel(const float* __restrict__ y, float* __restrict__ out, int top, int D, size_t total, const int* __restrict__ idx,
+                               const float* __restrict__ share, int real, const T* __restrict__ x, long long ldx, const float* __restrict__ b,
+                               int nb, size_t sb, const float* __restrict__ gate) {
   dep_launch();
   dep_wait();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -300,7 +315,15 @@ __global__ void combine_kernel(const float* __restrict__ y, float* __restrict__ 
   const size_t t = i / D;
   const int c = (int)(i - t * D);
   float s = 0.f;
-  for (int k = 0; k < top; ++k) s += y[(t * top + k) * D + c];
+  for (int k = 0; k < top; ++k) {
+    if (idx && idx[t * top + k] >= real) s += share[t * top + k] * to_f32(x[t * ldx + c]);
+    else s += y[(t * top + k) * D + c];
+  }
+  if (b) {
+    float v = b[i];
+    for (int p = 1; p < nb; ++p) v += b[(size_t)p * sb + i];
+    s += gate ? gate[t] * v : v;
+  }
   out[i] = s;
 }
 
@@ -324,7 +347,9 @@ extern "C" int llm_route(const void* x, long long ldx, const void* wr, const flo
 
 extern "C" int llm_route_grouped(const void* x, long long ldx, const void* wr, const float* correction, int n_tokens, int D, int E, int top,
                                  int n_groups, int keep, float norm_eps, int* idx, float* share, int dtype, int score_mode, int group_top, int normalize,
-                                 cudaStream_t stream) {
+                                 float weight_scale, float* gate_out, cudaStream_t stream) {
+  // weight_scale: the weights are multiplied by it at the end. gate_out (optional, float32 [tokens]): wr holds one more row behind the
+  // E router rows, and gate_out[t] = sigmoid(that row . x[t]), formed in float32 like the router's logits
   // score_mode 0: softmax over all experts, 1: sigmoid of each logit; group_top: a group's score is its largest choice score (1) or
   // the sum of its two largest (2); normalize 0: the chosen experts' scores are the weights as they are
   if (n_tokens == 0) return LLM_OK;
@@ -333,13 +358,13 @@ extern "C" int llm_route_grouped(const void* x, long long ldx, const void* wr, c
   LLM_REQUIRE(top <= 32 && E <= 4096, "route: at most 32 of 4096 experts a token (got %d of %d)", top, E);
   LLM_REQUIRE(n_groups >= 1 && keep >= 1 && keep <= n_groups && E % n_groups == 0, "route: %d experts do not form %d equal groups of which %d stay", E, n_groups, keep);
   LLM_REQUIRE((long long)keep * (E / n_groups) >= top, "route: %d groups of %d experts cannot give %d choices", keep, E / n_groups, top);
-  const size_t smem = (size_t)(2 * E + n_groups) * sizeof(float);
+  const size_t smem = (size_t)(2 * E + 1 + n_groups) * sizeof(float);
   if (dtype == LLM_F32)
     launch_kernel(route_grouped_kernel<float>, n_tokens, 256, smem, stream, (const float*)x, ldx, (const float*)wr, correction, D, E, top, n_groups,
-                  keep, norm_eps, idx, share, score_mode, group_top, normalize);
+                  keep, norm_eps, idx, share, score_mode, group_top, normalize, weight_scale, gate_out);
   else if (dtype == LLM_BF16)
     launch_kernel(route_grouped_kernel<bf16>, n_tokens, 256, smem, stream, (const bf16*)x, ldx, (const bf16*)wr, correction, D, E, top, n_groups,
-                  keep, norm_eps, idx, share, score_mode, group_top, normalize);
+                  keep, norm_eps, idx, share, score_mode, group_top, normalize, weight_scale, gate_out);
   else
     LLM_REQUIRE(false, "route: unknown dtype %d", dtype);
   LLM_CHECK_LAUNCH("route_grouped");
@@ -349,12 +374,13 @@ extern "C" int llm_route_grouped(const void* x, long long ldx, const void* wr, c
 extern "C" int llm_routed_tiles(int n_pairs, int E, int tile) { return (n_pairs + tile - 1) / tile + E; }
 
 extern "C" int llm_routed_group(const int* idx, int n_pairs, int E, int tile, int max_tiles, int* tile_expert, int* tile_rows,
-                                cudaStream_t stream) {
+                                int real_experts, cudaStream_t stream) {
+  // real_experts: idx may name experts real_experts .. E - 1 that have no matrices; their pairs enter no tile
   if (n_pairs == 0) return LLM_OK;
-  LLM_REQUIRE(n_pairs > 0 && E > 0 && tile > 0 && E <= 4096, "routed_group: bad sizes");
+  LLM_REQUIRE(n_pairs > 0 && E > 0 && tile > 0 && E <= 4096 && real_experts >= 0 && real_experts <= E, "routed_group: bad sizes");
   LLM_REQUIRE(max_tiles >= llm_routed_tiles(n_pairs, E, tile), "routed_group: room for %d tiles, %d may be needed", max_tiles,
               llm_routed_tiles(n_pairs, E, tile));
-  launch_kernel(group_kernel, 1, 1024, (size_t)3 * E * sizeof(int), stream, idx, n_pairs, E, tile, max_tiles, tile_expert, tile_rows);
+  launch_kernel(group_kernel, 1, 1024, (size_t)3 * E * sizeof(int), stream, idx, n_pairs, E, real_experts, tile, max_tiles, tile_expert, tile_rows);
   LLM_CHECK_LAUNCH("routed_group");
   return LLM_OK;
 }
@@ -362,16 +388,18 @@ extern "C" int llm_routed_group(const int* idx, int n_pairs, int E, int tile, in
 // a: rows picked by pair / a_div; w [E, N, K]; out rows at the pair's index. in_dtype: a and w; out_dtype: out.
 extern "C" int llm_routed_product(const void* a, long long lda, int a_div, const void* w, int N, int K, const int* tile_expert,
                                   const int* tile_rows, int max_tiles, void* out, long long ldo, int epilogue, const float* share,
-                                  int in_dtype, int out_dtype, cudaStream_t stream) {
+                                  int in_dtype, int out_dtype, int act, float p0, float p1, cudaStream_t stream) {
+  // act, p0, p1: the activation of epilogue 2 (0: silu; 2: both sides limited by p0, slope p1)
   if (max_tiles == 0) return LLM_OK;
   LLM_REQUIRE(N > 0 && K > 0 && a_div > 0 && max_tiles > 0 && max_tiles <= 65535, "routed_product: bad sizes");
   LLM_REQUIRE(epilogue == 0 || (epilogue == 1 && share) || (epilogue == 2 && N % 2 == 0), "routed_product: unknown epilogue %d", epilogue);
+  LLM_REQUIRE(act >= 0 && act <= 2, "routed_product: unknown activation %d", act);
   const long long ws = (long long)N * K;
   if (epilogue == 2) N /= 2;  // outputs: one for every (gate, up) pair of rows
   dim3 grid(ceil_div(N, RP_WARPS), max_tiles);
 #define LLM_RP(TA, TO)                                                                                                         \
   launch_kernel(routed_product_kernel<TA, TO>, grid, RP_WARPS * 32, 0, stream, (const TA*)a, lda, a_div, (const TA*)w, ws, N, K, \
-                tile_expert, tile_rows, (TO*)out, ldo, epilogue, share)
+                tile_expert, tile_rows, (TO*)out, ldo, epilogue, share, act, p0, p1)
   if (in_dtype == LLM_F32 && out_dtype == LLM_F32) LLM_RP(float, float);
   else if (in_dtype == LLM_BF16 && out_dtype == LLM_BF16) LLM_RP(bf16, bf16);
   else if (in_dtype == LLM_BF16 && out_dtype == LLM_F32) LLM_RP(bf16, float);
@@ -383,11 +411,20 @@ extern "C" int llm_routed_product(const void* a, long long lda, int a_div, const
 
 extern "C" int llm_routed_product_rows() { return RP_ROWS; }
 
-extern "C" int llm_routed_combine(const float* y, float* out, int n_tokens, int top, int D, cudaStream_t stream) {
+extern "C" int llm_routed_combine(const float* y, float* out, int n_tokens, int top, int D, const int* idx, const float* share, int real_experts,
+                                  const void* x, long long ldx, int x_dtype, const float* b, int nb, long long sb, const float* gate,
+                                  cudaStream_t stream) {
   if (n_tokens == 0) return LLM_OK;
   LLM_REQUIRE(n_tokens > 0 && top > 0 && D > 0, "routed_combine: bad sizes");
+  LLM_REQUIRE(idx == nullptr || (share && x), "routed_combine: identity experts need the weights and the input rows");
+  LLM_REQUIRE(b == nullptr || nb >= 1, "routed_combine: bad partial sums");
   const size_t total = (size_t)n_tokens * D;
-  launch_kernel(combine_kernel, ceil_div((long long)total, 256), 256, 0, stream, y, out, top, D, total);
+  if (x_dtype == LLM_BF16)
+    launch_kernel(combine_kernel<bf16>, ceil_div((long long)total, 256), 256, 0, stream, y, out, top, D, total, idx, share, real_experts,
+                  (const bf16*)x, ldx, b, nb, (size_t)sb, gate);
+  else
+    launch_kernel(combine_kernel<float>, ceil_div((long long)total, 256), 256, 0, stream, y, out, top, D, total, idx, share, real_experts,
+                  (const float*)x, ldx, b, nb, (size_t)sb, gate);
   LLM_CHECK_LAUNCH("routed_combine");
   return LLM_OK;
 }

@@ -6,7 +6,7 @@
 // with cp.async through a ring of three stages in shared memory; four warps of 16 rows each (m16n8k16). Every output row is
 // written at its pair's own index; a row's sum depends on K alone, not on the rest of its tile.
 // Epilogue 0: the exact (erf) gelu, bfloat16 out; 1: times the pair's router weight, float32 out; 2: the matrix holds a gate
-// row and its up row in turn (an even number of rows), out[p, n / 2] = silu(gate) * up, bfloat16 out.
+// row and its up row in turn (an even number of rows), out[p, n / 2] = act(gate, up) (silu(gate) * up, or both sides limited: common.cuh), bfloat16 out.
 // heads_product_mma: the same tile loop for a product per head over all tokens (the key and value maps of latent attention).
 #include "common.cuh"
 #include "mma_common.cuh"
@@ -25,7 +25,7 @@ template <typename TO, int EPI, int WM>
 __global__ void __launch_bounds__(RM_THREADS * WM)
     routed_product_mma_kernel(const bf16* __restrict__ a, long long lda, int a_div, const bf16* __restrict__ w, long long w_stride, int N,
                               int K, const int* __restrict__ tile_expert, const int* __restrict__ tile_rows, TO* __restrict__ out,
-                              long long ldo, const float* __restrict__ share) {
+                              long long ldo, const float* __restrict__ share, int act, float p0, float p1) {
   constexpr int ROWS = RM_ROWS * WM, COLS = RM_COLS * WM, THREADS = RM_THREADS * WM;
   extern __shared__ __align__(16) uint8_t smem_raw[];
   bf16 (*a_s)[ROWS][RM_LD] = reinterpret_cast<bf16 (*)[ROWS][RM_LD]>(smem_raw);
@@ -108,7 +108,7 @@ __global__ void __launch_bounds__(RM_THREADS * WM)
           if (EPI == 2) {  // the thread holds a gate column and, right of it, its up column
             if (el == 0) {
               const float u = acc[i][j][2 * half + 1];
-              dst[n / 2] = from_f32<TO>(v / (1.0f + expf(-v)) * u);
+              dst[n / 2] = from_f32<TO>(gated_value(v, u, act, p0, p1));
             }
             continue;
           }
@@ -132,7 +132,7 @@ template <typename TO, int EPI>
 __global__ void __launch_bounds__(RM_THREADS)
     routed_product_mma_few_kernel(const bf16* __restrict__ a, long long lda, int a_div, const bf16* __restrict__ w, long long w_stride, int N,
                                   int K, const int* __restrict__ tile_expert, const int* __restrict__ tile_rows, TO* __restrict__ out,
-                                  long long ldo, const float* __restrict__ share) {
+                                  long long ldo, const float* __restrict__ share, int act, float p0, float p1) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   bf16 (*a_s)[RS_ROWS][RM_LD] = reinterpret_cast<bf16 (*)[RS_ROWS][RM_LD]>(smem_raw);
   bf16 (*w_s)[RM_COLS][RM_LD] = reinterpret_cast<bf16 (*)[RM_COLS][RM_LD]>(smem_raw + (size_t)RS_STAGES * RS_ROWS * RM_LD * sizeof(bf16));
@@ -203,7 +203,7 @@ __global__ void __launch_bounds__(RM_THREADS)
         if (EPI == 2) {
           if (el == 0) {
             const float u = acc[j][2 * half + 1];
-            dst[n / 2] = from_f32<TO>(v / (1.0f + expf(-v)) * u);
+            dst[n / 2] = from_f32<TO>(gated_value(v, u, act, p0, p1));
           }
           continue;
         }
@@ -311,7 +311,7 @@ extern "C" int llm_routed_product_mma_supported(const void* a, long long lda, co
 
 template <typename TO, int EPI, int WM>
 int launch_routed(dim3 grid, cudaStream_t stream, const void* a, long long lda, int a_div, const void* w, long long ws, int N, int K,
-                  const int* tile_expert, const int* tile_rows, void* out, long long ldo, const float* share) {
+                  const int* tile_expert, const int* tile_rows, void* out, long long ldo, const float* share, int act, float p0, float p1) {
   static bool raised = false;
   if (!raised) {
     if (cudaFuncSetAttribute(routed_product_mma_kernel<TO, EPI, WM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(RM_SMEM * WM)) != cudaSuccess)
@@ -319,15 +319,17 @@ int launch_routed(dim3 grid, cudaStream_t stream, const void* a, long long lda, 
     raised = true;
   }
   launch_kernel(routed_product_mma_kernel<TO, EPI, WM>, grid, RM_THREADS * WM, RM_SMEM * WM, stream, (const bf16*)a, lda, a_div, (const bf16*)w,
-                ws, N, K, tile_expert, tile_rows, (TO*)out, ldo, share);
+                ws, N, K, tile_expert, tile_rows, (TO*)out, ldo, share, act, p0, p1);
   return 0;
 }
 
 // tile: the rows of a tile of tile_rows (64 or 128, as llm_routed_product_mma_rows said when the pairs were grouped).
 extern "C" int llm_routed_product_mma(const void* a, long long lda, int a_div, const void* w, int N, int K, const int* tile_expert,
                                       const int* tile_rows, int max_tiles, int tile, void* out, long long ldo, int epilogue,
-                                      const float* share, cudaStream_t stream) {
+                                      const float* share, int act, float p0, float p1, cudaStream_t stream) {
+  // act, p0, p1: the activation of epilogue 2 (0: silu; 2: both sides limited by p0, slope p1)
   if (max_tiles == 0) return LLM_OK;
+  LLM_REQUIRE(act >= 0 && act <= 2, "routed_product_mma: unknown activation %d", act);
   LLM_REQUIRE(llm_routed_product_mma_supported(a, lda, w, K), "routed_product_mma: operands must be 16-byte aligned with K and the row stride multiples of 8");
   LLM_REQUIRE(N > 0 && a_div > 0 && max_tiles > 0 && max_tiles <= 65535, "routed_product_mma: bad sizes");
   LLM_REQUIRE(tile == RS_ROWS || tile == RM_ROWS || tile == 2 * RM_ROWS, "routed_product_mma: tiles of %d rows (16, 64 or 128)", tile);
@@ -345,13 +347,13 @@ extern "C" int llm_routed_product_mma(const void* a, long long lda, int a_div, c
     const long long wsf = (long long)N * K;
     if (epilogue == 0)
       launch_kernel(routed_product_mma_few_kernel<bf16, 0>, grid_few, RM_THREADS, RS_SMEM, stream, (const bf16*)a, lda, a_div, (const bf16*)w, wsf,
-                    N, K, tile_expert, tile_rows, (bf16*)out, ldo, share);
+                    N, K, tile_expert, tile_rows, (bf16*)out, ldo, share, act, p0, p1);
     else if (epilogue == 2)
       launch_kernel(routed_product_mma_few_kernel<bf16, 2>, grid_few, RM_THREADS, RS_SMEM, stream, (const bf16*)a, lda, a_div, (const bf16*)w, wsf,
-                    N, K, tile_expert, tile_rows, (bf16*)out, ldo, share);
+                    N, K, tile_expert, tile_rows, (bf16*)out, ldo, share, act, p0, p1);
     else
       launch_kernel(routed_product_mma_few_kernel<float, 1>, grid_few, RM_THREADS, RS_SMEM, stream, (const bf16*)a, lda, a_div, (const bf16*)w, wsf,
-                    N, K, tile_expert, tile_rows, (float*)out, ldo, share);
+                    N, K, tile_expert, tile_rows, (float*)out, ldo, share, act, p0, p1);
     LLM_CHECK_LAUNCH("routed_product_mma");
     return LLM_OK;
   }
@@ -360,14 +362,14 @@ extern "C" int llm_routed_product_mma(const void* a, long long lda, int a_div, c
   const long long ws = (long long)N * K;
   int rc;
   if (epilogue == 0)
-    rc = wm == 2 ? launch_routed<bf16, 0, 2>(grid, stream, a, lda, a_div, w, ws, N, K, tile_expert, tile_rows, out, ldo, share)
-                 : launch_routed<bf16, 0, 1>(grid, stream, a, lda, a_div, w, ws, N, K, tile_expert, tile_rows, out, ldo, share);
+    rc = wm == 2 ? launch_routed<bf16, 0, 2>(grid, stream, a, lda, a_div, w, ws, N, K, tile_expert, tile_rows, out, ldo, share, act, p0, p1)
+                 : launch_routed<bf16, 0, 1>(grid, stream, a, lda, a_div, w, ws, N, K, tile_expert, tile_rows, out, ldo, share, act, p0, p1);
   else if (epilogue == 2)
-    rc = wm == 2 ? launch_routed<bf16, 2, 2>(grid, stream, a, lda, a_div, w, ws, N, K, tile_expert, tile_rows, out, ldo, share)
-                 : launch_routed<bf16, 2, 1>(grid, stream, a, lda, a_div, w, ws, N, K, tile_expert, tile_rows, out, ldo, share);
+    rc = wm == 2 ? launch_routed<bf16, 2, 2>(grid, stream, a, lda, a_div, w, ws, N, K, tile_expert, tile_rows, out, ldo, share, act, p0, p1)
+                 : launch_routed<bf16, 2, 1>(grid, stream, a, lda, a_div, w, ws, N, K, tile_expert, tile_rows, out, ldo, share, act, p0, p1);
   else
-    rc = wm == 2 ? launch_routed<float, 1, 2>(grid, stream, a, lda, a_div, w, ws, N, K, tile_expert, tile_rows, out, ldo, share)
-                 : launch_routed<float, 1, 1>(grid, stream, a, lda, a_div, w, ws, N, K, tile_expert, tile_rows, out, ldo, share);
+    rc = wm == 2 ? launch_routed<float, 1, 2>(grid, stream, a, lda, a_div, w, ws, N, K, tile_expert, tile_rows, out, ldo, share, act, p0, p1)
+                 : launch_routed<float, 1, 1>(grid, stream, a, lda, a_div, w, ws, N, K, tile_expert, tile_rows, out, ldo, share, act, p0, p1);
   LLM_REQUIRE(rc == 0, "routed_product_mma: cannot raise the shared memory limit");
   LLM_CHECK_LAUNCH("routed_product_mma");
   return LLM_OK;

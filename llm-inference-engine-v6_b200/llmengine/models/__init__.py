@@ -1,2 +1,2 @@
 """Architectures: each module registers one name of config.json `architectures` (or `architecture`)."""
-from . import llama, selinex, vapelix, zulopel  # noqa: F401
+from . import llama, selinex, sogutar, vapelix, zulopel  # noqa: F401

@@ -182,8 +182,9 @@ class CudaOps:
 
     def rmsnorm(self, h: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
                 delta: Optional[torch.Tensor] = None, rows: Optional[torch.Tensor] = None,
-                n_rows: Optional[int] = None, write_back: bool = True) -> torch.Tensor:
-        """x = h[r] (+ delta[r], or + sum_p delta[p][r] for a 3-d delta); out = (w*x)/rms(x).
+                n_rows: Optional[int] = None, write_back: bool = True, center: bool = False) -> torch.Tensor:
+        """x = h[r] (+ delta[r], or + sum_p delta[p][r] for a 3-d delta); out = (w*x)/rms(x), or with `center` (a layer norm
+        without bias) out = w * (x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps).
         With `delta` and write_back, h[r] is replaced by x (the fused residual sum).
         With `rows` (int32), output row i reads source row rows[i] and h is left as it is."""
         _need(h, "rmsnorm.h", torch.float32); _need(weight, "rmsnorm.weight", torch.float32); _need(out, "rmsnorm.out")
@@ -203,7 +204,7 @@ class CudaOps:
         self._check(lib.llm_rmsnorm(_ptr(h), _ptr(delta), c_int(n_part), c_longlong(pstride), _ptr(weight),
                                     _ptr(rows), _ptr(out), c_int(dtype_code(out.dtype)), c_int(n_out), c_int(dim),
                                     c_float(eps), c_int(1 if (write_back and delta is not None) else 0),
-                                    _stream()), lib)
+                                    c_int(1 if center else 0), _stream()), lib)
         return out
 
     def residual_add(self, h: torch.Tensor, delta: torch.Tensor, n_rows: Optional[int] = None) -> torch.Tensor:
@@ -215,6 +216,14 @@ class CudaOps:
         self._check(lib.llm_residual_add(_ptr(h), _ptr(delta), c_int(n_part), c_longlong(pstride), c_longlong(n),
                                          _stream()), lib)
         return h
+
+    def softcap(self, x: torch.Tensor, cap: float) -> torch.Tensor:
+        """x <- cap * tanh(x / cap) in place (float32)."""
+        _need(x, "softcap.x", torch.float32)
+        assert x.is_contiguous() and cap > 0
+        lib = self.lib()
+        self._check(lib.llm_softcap(_ptr(x), c_longlong(x.numel()), c_float(cap), _stream()), lib)
+        return x
 
     # what a gated feed-forward may apply to its gate; "clamped_swish" comes as ("clamped_swish", limit, slope):
     # g <- min(g, limit), u <- clamp(u, -limit, limit), g * sigmoid(slope * g) * (u + 1)
@@ -956,19 +965,23 @@ class CudaOps:
         self._check(lib.llm_route(_ptr(x), c_longlong(x.stride(0)), _ptr(w), _ptr(bias), c_int(n), c_int(D), c_int(E), c_int(top),
                                   _ptr(idx), _ptr(share), c_int(dtype_code(x.dtype)), _stream()), lib)
 
-    ROUTED_EPILOGUES = {"gelu": 0, "share": 1, "silu_pairs": 2}
+    ROUTED_EPILOGUES = {"gelu": 0, "share": 1, "silu_pairs": 2, "gated_pairs": 2}
 
     def route_grouped(self, x: torch.Tensor, w: torch.Tensor, correction: Optional[torch.Tensor], top: int, groups: int, keep: int,
                       norm_eps: float, idx: torch.Tensor, share: torch.Tensor, score: str = "softmax", group_top: int = 1,
-                      normalize: bool = True) -> None:
+                      normalize: bool = True, weight_scale: float = 1.0, gate_out: Optional[torch.Tensor] = None) -> None:
         """Per token: s = softmax(w x) over all experts, or (score "sigmoid") the sigmoid of every logit (float32); choice = s +
         correction; only experts of the `keep` of `groups` equal groups of neighbours with the largest group scores can be chosen
         (a group's score: its largest choice score, or with group_top 2 the sum of its two largest; the others count as minus
         infinity); idx [n, top] = the largest choice scores among them (the lower index wins a tie); share [n, top] = their s
-        divided by (the sum of the chosen s + norm_eps), or as they are (normalize False)."""
+        divided by (the sum of the chosen s + norm_eps), or as they are (normalize False), then times weight_scale. With gate_out
+        (float32 [n]) w holds one more row behind the experts' rows and gate_out[t] = sigmoid(that row . x[t]) in float32."""
         _need(x, "route.x"); _need(w, "route.w", x.dtype); _need(idx, "route.idx", torch.int32); _need(share, "route.share", torch.float32)
         n, D = x.shape
-        E = w.shape[0]
+        E = w.shape[0] - (1 if gate_out is not None else 0)
+        if gate_out is not None:
+            _need(gate_out, "route.gate_out", torch.float32)
+            assert gate_out.is_contiguous() and gate_out.numel() >= n
         assert w.is_contiguous() and w.shape[1] == D and idx.is_contiguous() and share.is_contiguous()
         assert idx.shape == (n, top) and share.shape == (n, top)
         if correction is not None:
@@ -978,7 +991,7 @@ class CudaOps:
         self._check(lib.llm_route_grouped(_ptr(x), c_longlong(x.stride(0)), _ptr(w), _ptr(correction), c_int(n), c_int(D), c_int(E),
                                           c_int(top), c_int(groups), c_int(keep), c_float(norm_eps), _ptr(idx), _ptr(share),
                                           c_int(dtype_code(x.dtype)), c_int({"softmax": 0, "sigmoid": 1}[score]), c_int(group_top),
-                                          c_int(1 if normalize else 0), _stream()), lib)
+                                          c_int(1 if normalize else 0), c_float(weight_scale), _ptr(gate_out), _stream()), lib)
 
     def routed_tile_rows(self, n_tokens: int = 0, dtype: Optional[torch.dtype] = None, inner=(), per_expert: float = 0.0) -> int:
         """Rows of a tile of the per-expert products: the tensor-core kernel's in bfloat16 when every product's inner
@@ -988,9 +1001,10 @@ class CudaOps:
             return int(self.lib("tensorcore").llm_routed_product_mma_rows(c_int(int(per_expert))))
         return int(self.lib().llm_routed_product_rows())
 
-    def routed_group(self, idx: torch.Tensor, experts: int, tile: int, ws, tag: str):
+    def routed_group(self, idx: torch.Tensor, experts: int, tile: int, ws, tag: str, real_experts: Optional[int] = None):
         """Sorts the step's (token, choice) pairs by expert into tiles of `tile` rows -> (tile_expert [tiles] with -1 for
-        unused tiles, tile_rows [tiles, tile] with -1 for padding); a pair is token * top + choice."""
+        unused tiles, tile_rows [tiles, tile] with -1 for padding); a pair is token * top + choice. Pairs of experts from
+        real_experts on (experts without matrices, dealt with by routed_combine) enter no tile."""
         _need(idx, "routed_group.idx", torch.int32)
         lib = self.lib()
         pairs = idx.numel()
@@ -998,18 +1012,21 @@ class CudaOps:
         tile_expert = ws.get(tag + ".tile_expert", (tiles,), torch.int32)
         tile_rows = ws.get(tag + ".tile_rows", (tiles, tile), torch.int32)
         self._check(lib.llm_routed_group(_ptr(idx), c_int(pairs), c_int(experts), c_int(tile), c_int(tiles), _ptr(tile_expert),
-                                         _ptr(tile_rows), _stream()), lib)
+                                         _ptr(tile_rows), c_int(experts if real_experts is None else real_experts), _stream()), lib)
         return tile_expert, tile_rows
 
     def routed_product(self, a: torch.Tensor, a_div: int, w: torch.Tensor, tile_expert: torch.Tensor, tile_rows: torch.Tensor,
-                       out: torch.Tensor, epilogue: str, share: Optional[torch.Tensor] = None) -> torch.Tensor:
+                       out: torch.Tensor, epilogue: str, share: Optional[torch.Tensor] = None, act="silu") -> torch.Tensor:
         """For every pair p of every tile (expert e): out[p, :] = epi(w[e] a[p // a_div, :]); w [E, N, K]. epilogue "gelu":
         the exact (erf) gelu; "share": times share[p] (float32, flat); "silu_pairs": w holds a gate row and its up row in turn
-        ([E, 2 F, K]) and out[p, f] = silu(gate_f) * up_f ([pairs, F])."""
+        ([E, 2 F, K]) and out[p, f] = silu(gate_f) * up_f ([pairs, F]); "gated_pairs": the same rows with the activation `act`
+        of a gated feed-forward (ACTIVATIONS; ("clamped_swish", limit, slope) limits both sides)."""
         _need(a, "routed_product.a"); _need(w, "routed_product.w", a.dtype); _need(out, "routed_product.out")
         E, N, K = w.shape
-        assert w.is_contiguous() and a.shape[1] == K and out.shape[1] == (N // 2 if epilogue == "silu_pairs" else N)
-        assert epilogue != "silu_pairs" or N % 2 == 0
+        pairs = epilogue in ("silu_pairs", "gated_pairs")
+        assert w.is_contiguous() and a.shape[1] == K and out.shape[1] == (N // 2 if pairs else N)
+        assert not pairs or N % 2 == 0
+        act_args = self._act_args(act if epilogue == "gated_pairs" else "silu")
         if epilogue == "share":
             _need(share, "routed_product.share", torch.float32)
         if a.dtype == torch.bfloat16 and self.tensor_cores and tile_rows.shape[1] != self.routed_tile_rows():
@@ -1019,23 +1036,42 @@ class CudaOps:
                                                    _ptr(tile_expert), _ptr(tile_rows), c_int(tile_expert.numel()),
                                                    c_int(tile_rows.shape[1]), _ptr(out),
                                                    c_longlong(out.stride(0)), c_int(self.ROUTED_EPILOGUES[epilogue]), _ptr(share),
-                                                   _stream()), lib)
+                                                   *act_args, _stream()), lib)
             return out
         assert tile_rows.shape[1] == self.routed_tile_rows()
         lib = self.lib()
         self._check(lib.llm_routed_product(_ptr(a), c_longlong(a.stride(0)), c_int(a_div), _ptr(w), c_int(N), c_int(K), _ptr(tile_expert),
                                            _ptr(tile_rows), c_int(tile_expert.numel()), _ptr(out), c_longlong(out.stride(0)),
                                            c_int(self.ROUTED_EPILOGUES[epilogue]), _ptr(share), c_int(dtype_code(a.dtype)),
-                                           c_int(dtype_code(out.dtype)), _stream()), lib)
+                                           c_int(dtype_code(out.dtype)), *act_args, _stream()), lib)
         return out
 
-    def routed_combine(self, y: torch.Tensor, out: torch.Tensor, top: int) -> torch.Tensor:
-        """out[t, :] = sum_k y[t * top + k, :] in index order; float32."""
+    def routed_combine(self, y: torch.Tensor, out: torch.Tensor, top: int, identity=None, extra: Optional[torch.Tensor] = None,
+                       extra_gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """out[t, :] = sum_k y[t * top + k, :] in index order; float32. identity = (idx [n, top] int32, share [n, top] float32,
+        real_experts, x [n, D]): a choice whose expert is real_experts or higher is an identity expert and adds share[t, k] * x[t]
+        in place of its row of y (which nobody wrote). extra: float32 sums [n, D] or [parts, n, D] added behind the chosen ones
+        (an expert that every token uses), times extra_gate[t] (float32 [n]) if given."""
         _need(y, "routed_combine.y", torch.float32); _need(out, "routed_combine.out", torch.float32)
         n, D = out.shape
         assert y.is_contiguous() and out.is_contiguous() and y.shape == (n * top, D)
+        id_args = [c_void_p(0), c_void_p(0), c_int(0), c_void_p(0), c_longlong(0), c_int(F32)]
+        if identity is not None:
+            idx, share, real, x = identity
+            _need(idx, "routed_combine.idx", torch.int32); _need(share, "routed_combine.share", torch.float32); _need(x, "routed_combine.x")
+            assert idx.is_contiguous() and share.is_contiguous() and idx.shape == (n, top) and share.shape == (n, top) and x.shape[0] >= n and x.shape[1] == D
+            id_args = [_ptr(idx), _ptr(share), c_int(real), _ptr(x), c_longlong(x.stride(0)), c_int(dtype_code(x.dtype))]
+        ex_args = [c_void_p(0), c_int(0), c_longlong(0), c_void_p(0)]
+        if extra is not None:
+            _need(extra, "routed_combine.extra", torch.float32)
+            assert extra.is_contiguous() and extra.shape[-1] == D and extra.shape[-2] == n
+            if extra_gate is not None:
+                _need(extra_gate, "routed_combine.gate", torch.float32)
+                assert extra_gate.is_contiguous() and extra_gate.numel() >= n
+            ex_args = [_ptr(extra), c_int(extra.shape[0] if extra.dim() == 3 else 1), c_longlong(extra.stride(0) if extra.dim() == 3 else 0),
+                       _ptr(extra_gate)]
         lib = self.lib()
-        self._check(lib.llm_routed_combine(_ptr(y), _ptr(out), c_int(n), c_int(top), c_int(D), _stream()), lib)
+        self._check(lib.llm_routed_combine(_ptr(y), _ptr(out), c_int(n), c_int(top), c_int(D), *id_args, *ex_args, _stream()), lib)
         return out
 
     # ------------------------------------------------------------------ norms on a sub-layer's output
@@ -1072,9 +1108,12 @@ class CudaOps:
     def qkv_prep(self, parts: torch.Tensor, heads: int, kv_heads: int, dk: int, dv: int, q_norm: Optional[torch.Tensor],
                  k_norm: Optional[torch.Tensor], eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], batch,
                  block_table: torch.Tensor, q_out: torch.Tensor, kcache: Optional[torch.Tensor], vcache: Optional[torch.Tensor],
-                 mix_role: int = 0, mix_weight: Optional[torch.Tensor] = None, v_first: Optional[torch.Tensor] = None) -> None:
+                 mix_role: int = 0, mix_weight: Optional[torch.Tensor] = None, v_first: Optional[torch.Tensor] = None,
+                 norm_wide: bool = False) -> None:
         """From the float32 sums `parts` [p, n, width] of a product whose columns begin with [q: heads * dk | k: kv_heads * dk |
-        v: kv_heads * dv]: RMS norm of every query and key head with the weights q_norm / k_norm [dk] (None: no norm), rotation
+        v: kv_heads * dv] (kv_heads 0: queries alone, nothing to write): RMS norm of every query and key head with the weights
+        q_norm / k_norm [dk] (None: no norm), or with norm_wide ONE RMS norm over all query heads' numbers together with q_norm
+        [heads * dk] and one over all key heads' with k_norm [kv_heads * dk]; rotation
         of the first 2 * cos.shape[1] numbers of each head (half-split pairs) at the token's position, q into q_out
         [n, heads * dk], k and v into the token's page of kcache [pages, kv_heads, page, dk] / vcache [.., dv] (None: no write).
         mix_role 1: the values are also left in v_first (float32 [n, kv_heads * dv]); 2: v <- (1 - m) v + m v_first before
@@ -1087,7 +1126,8 @@ class CudaOps:
             if t is not None:
                 _need(t, "qkv_prep." + name, torch.float32)
                 assert t.is_contiguous()
-        assert (q_norm is None or q_norm.numel() == dk) and (k_norm is None or k_norm.numel() == dk)
+        wide = (heads, kv_heads) if norm_wide else (1, 1)
+        assert (q_norm is None or q_norm.numel() == wide[0] * dk) and (k_norm is None or kv_heads == 0 or k_norm.numel() == wide[1] * dk)
         page = 1
         if kcache is not None:
             _need(kcache, "qkv_prep.kcache", q_out.dtype); _need(vcache, "qkv_prep.vcache", q_out.dtype)
@@ -1102,7 +1142,7 @@ class CudaOps:
                                      _ptr(cos), _ptr(sin), _ptr(batch.positions), _ptr(batch.token_seq), _ptr(block_table),
                                      c_int(block_table.shape[1]), _ptr(q_out), c_longlong(q_out.stride(0)), _ptr(kcache), _ptr(vcache),
                                      c_int(page), c_int(mix_role), _ptr(mix_weight), _ptr(v_first), c_int(dtype_code(q_out.dtype)),
-                                     c_int(n), _stream()), lib)
+                                     c_int(n), c_int(1 if norm_wide else 0), _stream()), lib)
 
     def gated_attention(self, q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, batch, block_table: torch.Tensor,
                         out: torch.Tensor, nq: int, nkv: int, dk: int, dv: int, scale: float, window: int = 0, chunk: int = 0,
@@ -1308,14 +1348,15 @@ class CudaOps:
 
     def linear_state(self, rule: str, q, q_off: int, k, k_off: int, v, v_off: int, decay: torch.Tensor, decay_off: int,
                      bonus: Optional[torch.Tensor], state: torch.Tensor, batch, out: torch.Tensor, heads: int, kv_heads: int, dk: int,
-                     dv: int, q_scale: float = 1.0, unit_eps: float = -1.0) -> torch.Tensor:
+                     dv: int, q_scale: float = 1.0, unit_eps: float = -1.0, decay_const: bool = False) -> torch.Tensor:
         """Token after token of every request, per head a matrix S [dk, dv] (float32, in the request's slot of `state`):
         "decay_write_read": S <- diag(a) S + k v^T, o = S^T q; "bonus_read_decay_write": o = (S + diag(bonus) k v^T)^T q, then
         S <- diag(a) S + k v^T; "delta": S <- g S, w = beta (v - S^T k), S <- S + k w^T, o = S^T q with q and k made unit vectors
         per head first (x / sqrt(sum x^2 + unit_eps); unit_eps < 0: as they are). q is multiplied by q_scale. q, k, v: float32 sums
         ([parts, n, width] or [n, width]) read at column offsets, q and k with kv_heads heads of dk (head h reads head
         h // (heads / kv_heads)), v with heads of dv. decay: float32 rows; at decay_off a number per (head, key channel), or for
-        "delta" [g: heads | beta: heads]. out float32 [n, heads * dv]."""
+        "delta" [g: heads | beta: heads]; with decay_const a single row that holds for every token (decays that are constants
+        of the model). out float32 [n, heads * dv]."""
         _need(decay, "linear_state.decay", torch.float32); _need(state, "linear_state.state", torch.float32); _need(out, "linear_state.out", torch.float32)
         assert decay.is_contiguous() and decay.dim() == 2 and state.is_contiguous() and out.is_contiguous() and out.shape[1] == heads * dv
         assert tuple(state.shape[1:]) == tuple(self.linear_state_shape(heads, dk, dv))
@@ -1327,7 +1368,26 @@ class CudaOps:
                                          *self._sums(k, k_off, "linear_state.k"), *self._sums(v, v_off, "linear_state.v"), _ptr(decay),
                                          c_int(decay.shape[1]), c_int(decay_off), _ptr(bonus), _ptr(state), _ptr(batch.seq_qoff),
                                          _ptr(batch.seq_ntok), _ptr(batch.seq_slot), _ptr(out), c_int(batch.n_tokens), c_int(batch.n_seqs), c_int(heads),
-                                         c_int(kv_heads), c_int(dk), c_int(dv), c_float(q_scale), c_float(unit_eps), _stream()), lib)
+                                         c_int(kv_heads), c_int(dk), c_int(dv), c_float(q_scale), c_float(unit_eps), c_int(1 if decay_const else 0),
+                                         _stream()), lib)
+        return out
+
+    def rotate_sums(self, x, x_off: int, heads: int, dk: int, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], positions: torch.Tensor,
+                    out: torch.Tensor, n_tokens: int, scaled_from: Optional[int] = None, scale: float = 1.0) -> torch.Tensor:
+        """out[t] (float32 [n, heads * dk]) = the `heads` heads of dk numbers that lie side by side from column x_off of the float32
+        sums x, the first 2 * cos.shape[1] numbers of every head rotated (half-split pairs) at the token's position; heads from
+        `scaled_from` on are then multiplied by `scale`. Nothing is rounded: for mixers whose recurrence reads rotated queries and keys."""
+        _need(out, "rotate_sums.out", torch.float32); _need(positions, "rotate_sums.positions", torch.int32)
+        assert out.is_contiguous() and out.shape[1] == heads * dk and out.shape[0] >= n_tokens
+        rot = 0 if cos is None else 2 * cos.shape[1]
+        for t in (cos, sin):
+            if t is not None:
+                _need(t, "rotate_sums.table", torch.float32)
+                assert t.is_contiguous()
+        lib = self.lib()
+        self._check(lib.llm_rotate_sums(*self._sums(x, x_off, "rotate_sums.x"), c_int(heads), c_int(dk), c_int(rot), _ptr(cos), _ptr(sin),
+                                        _ptr(positions), _ptr(out), c_int(n_tokens), c_int(heads if scaled_from is None else scaled_from),
+                                        c_float(scale), _stream()), lib)
         return out
 
     def token_shift(self, x: torch.Tensor, mu: torch.Tensor, shift_state: torch.Tensor, batch, out: torch.Tensor) -> torch.Tensor:

@@ -1,7 +1,7 @@
 """Arrangement of parts in a layer. "pre_norm": h += mixer(norm1(h)); h += feed_forward(norm2(h))
 (src/engine.cpp:307-413). The residual sums are fused into the norm that follows them.
-"parallel": h += mixer(norm1(h)) + feed_forward(norm2(h)), both norms of the same h; then an optional
-input from the tokens themselves, h += token_input(h).
+"parallel": h += mixer(norm1(h)) + feed_forward(norm2(h)), both norms of the same h (or, without a norm2, ONE norm whose
+rows both sub-layers read); then an optional input from the tokens themselves, h += token_input(h).
 "post_norm": the sub-layers read h itself and the norms sit on their outputs, each followed by an optional per-column
 layer scale: h += scale1 * norm1(mixer(h)); h += scale2 * norm2(feed_forward(h)).
 "sandwich": a norm before and one after each sub-layer, and one multiplier on everything that is added:
@@ -76,7 +76,8 @@ class ParallelBlock(Block):
         self.mixer = build_part("mixer", spec.mixer, env)
         self.feed_forward = self.norm2 = self.token_input = None
         if spec.feed_forward is not None:
-            self.norm2 = build_part("norm", spec.norm2, env)
+            if spec.norm2 is not None:  # None: the feed-forward reads the first norm's rows
+                self.norm2 = build_part("norm", spec.norm2, env)
             self.feed_forward = build_part("feed_forward", spec.feed_forward, env)
         if spec.token_input is not None:
             self.token_input = build_part("token_input", spec.token_input, env)
@@ -86,7 +87,7 @@ class ParallelBlock(Block):
         out: List[TensorNeed] = []
         subs = [("norm", spec.norm1), ("mixer", spec.mixer)]
         if spec.feed_forward is not None:
-            subs += [("norm", spec.norm2), ("feed_forward", spec.feed_forward)]
+            subs += ([("norm", spec.norm2)] if spec.norm2 is not None else []) + [("feed_forward", spec.feed_forward)]
         if spec.token_input is not None:
             subs.append(("token_input", spec.token_input))
         for cat, sub in subs:
@@ -113,8 +114,11 @@ class ParallelBlock(Block):
         # the second norm's rows go to a buffer of their own: the mixer runs first and both read the same stream
         x2 = None
         if self.feed_forward is not None:
-            x2 = ctx.ws.get("block.norm2_out", (n, res.h.shape[1]), self.env.dtype)
-            self.norm2.run(res.h, ctx, None, n, out=x2)
+            if self.norm2 is None:
+                x2 = x1  # one norm for both: the mixer leaves its input as it is
+            else:
+                x2 = ctx.ws.get("block.norm2_out", (n, res.h.shape[1]), self.env.dtype)
+                self.norm2.run(res.h, ctx, None, n, out=x2)
         a = self.mixer.forward(x1, ctx, cache)
         b = self.feed_forward.forward(x2, ctx) if self.feed_forward is not None else None
         if self.token_input is None:

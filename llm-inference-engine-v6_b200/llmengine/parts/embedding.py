@@ -13,7 +13,7 @@ from typing import List
 import torch
 
 from .base import Embedding, Head, NormalizedRows
-from .registry import register_part
+from .registry import build_part, part_class, register_part
 from .spec import EmbeddingSpec, HeadSpec, TensorNeed
 
 
@@ -59,6 +59,36 @@ class TokenLookup(Embedding):
         return self.env.ops.embed(self.table, ctx.token_ids, out, **({} if scale == 1.0 else {"scale": scale}))
 
 
+class NormedTokenLookup(TokenLookup):
+    """The table row of each token id, then a norm of its own over the row: the float32 stream starts normalised. The norm is any
+    registered norm (EmbeddingSpec.norm); it reads the gathered rows and writes the stream in float32."""
+
+    def __init__(self, spec: EmbeddingSpec, env):
+        super().__init__(spec, env)
+        if spec.norm is None:
+            raise ValueError("embedding 'lookup_normed' needs a norm")
+        self.norm = build_part("norm", spec.norm, env)
+
+    @staticmethod
+    def tensor_needs(spec: EmbeddingSpec) -> List[TensorNeed]:
+        return TokenLookup.tensor_needs(spec) + list(part_class("norm", spec.norm.kind).tensor_needs(spec.norm))
+
+    def subparts(self):
+        return (self.norm,)
+
+    def load(self, tensors) -> None:
+        super().load(tensors)
+        self.norm.load(tensors)
+
+    def forward(self, ctx) -> torch.Tensor:
+        return self.lookup(ctx, ctx.ws.get("model.residual", (ctx.n_tokens, self.spec.dim), torch.float32))
+
+    def lookup(self, ctx, out: torch.Tensor) -> torch.Tensor:
+        raw = ctx.ws.get("embedding.rows", (ctx.n_tokens, self.spec.dim), torch.float32)
+        super().lookup(ctx, raw)
+        return self.norm.run(raw, ctx, None, ctx.n_tokens, out=out)
+
+
 class LinearHead(Head):
     def __init__(self, spec: HeadSpec, env):
         super().__init__(spec, env)
@@ -79,16 +109,23 @@ class LinearHead(Head):
     def forward(self, x, ctx) -> torch.Tensor:
         n = x.n if isinstance(x, NormalizedRows) else x.shape[0]
         logits = ctx.ws.get("model.logits", (max(n, 1), self.spec.vocab_size), torch.float32)[:n]
+        cap = float(getattr(self.spec, "softcap", 0.0) or 0.0)
+        done = False
         if isinstance(x, NormalizedRows):
             ops = self.env.ops
             if x.prescaled is not None and n and self.wants_lazy_norm(ctx) and ops.can_meet(x.prescaled[:n], self.weight):
                 # the product runs on weight * rows and divides by the rows' root mean square in its epilogue
-                return ops.gemm_scaled(x.prescaled[:n], self.weight, logits, x.row_scale(ops))
-            x = x.dense(ctx)
-        if n:
+                ops.gemm_scaled(x.prescaled[:n], self.weight, logits, x.row_scale(ops))
+                done = True
+            else:
+                x = x.dense(ctx)
+        if n and not done:
             self.env.ops.gemm(x, self.weight, logits)
+        if n and cap > 0.0:
+            self.env.ops.softcap(logits, cap)  # logits <- cap * tanh(logits / cap), float32
         return logits
 
 
 register_part("embedding", "lookup", TokenLookup)
+register_part("embedding", "lookup_normed", NormedTokenLookup)
 register_part("head", "linear", LinearHead)

@@ -8,6 +8,8 @@ With h the mixer's input, per token at position p:
     score_a(i, j) = (q_a(i) . k_b(j)) * scale,  b = a // (H / G),  j <= i in the same chunk (and inside the window)
     p_a(i, j) = exp(score) / (sum_j exp(score) + exp(sink_a))   the sink only enlarges the denominator
     out = Wo ((heads' results side by side) * sigmoid(g))       g: a gate a number of the result, or (gate_per_head) one a head
+With norm_scope "projection" the two norms are over all of q and all of k at once (weights of the projections' sizes). A layer
+without keys and values of its own (own_kv False) forms queries only and reads the cache of the run its LayerRun names.
 Norms, rotation, scores, softmax and the gate are float32 in both engine precisions. v_first are the values that the
 first layer with value mixing computed for the same tokens in the same step: that layer leaves them in the step
 context (`ctx.shared`), the later ones read them there.
@@ -36,6 +38,10 @@ class GatedAttention(Mixer):
             raise ValueError(f"gated attention: {spec.num_heads} heads cannot share {spec.num_kv_heads} key/value heads")
         if spec.window < 0 or spec.chunk < 0:
             raise ValueError("gated attention: window and chunk must be >= 0")
+        if spec.norm_scope not in ("head", "projection"):
+            raise ValueError("gated attention: norm_scope is 'head' or 'projection'")
+        if not spec.own_kv and (spec.value_mix is not None or spec.k_norm):
+            raise ValueError("gated attention: a layer that borrows keys and values has no key norm and mixes no values")
         if spec.value_mix not in (None, "first", "mix") or (spec.value_mix == "mix" and not spec.value_mix_weight):
             raise ValueError("gated attention: value_mix is None, 'first' or 'mix' (with the name of its weight)")
         self.position = build_part("position", spec.position, env)
@@ -50,13 +56,15 @@ class GatedAttention(Mixer):
     @staticmethod
     def tensor_needs(spec: GatedAttentionSpec) -> List[TensorNeed]:
         H, G, dk, dv = spec.num_heads, spec.num_kv_heads, spec.head_dim, spec.value_dim
-        out = [TensorNeed(spec.q_weight, (H * dk, spec.hidden)), TensorNeed(spec.k_weight, (G * dk, spec.hidden)),
-               TensorNeed(spec.v_weight, (G * dv, spec.hidden)), TensorNeed(spec.o_weight, (spec.hidden, H * dv))]
+        out = [TensorNeed(spec.q_weight, (H * dk, spec.hidden)), TensorNeed(spec.o_weight, (spec.hidden, H * dv))]
+        if spec.own_kv:
+            out += [TensorNeed(spec.k_weight, (G * dk, spec.hidden)), TensorNeed(spec.v_weight, (G * dv, spec.hidden))]
         if spec.gate_weight:
             out.append(TensorNeed(spec.gate_weight, (H if spec.gate_per_head else H * dv, spec.hidden)))
-        for name in (spec.q_norm, spec.k_norm):
+        wide = spec.norm_scope == "projection"
+        for name, heads in ((spec.q_norm, H), (spec.k_norm, G)):
             if name:
-                out.append(TensorNeed(name, (dk,), "float32", init="around_one"))
+                out.append(TensorNeed(name, (heads * dk if wide else dk,), "float32", init="around_one"))
         if spec.sink:
             out.append(TensorNeed(spec.sink, (H,), "float32"))
         if spec.value_mix_weight:  # read by "mix" layers; a "first" layer's file may carry one that nobody uses
@@ -68,7 +76,9 @@ class GatedAttention(Mixer):
 
     def cache_needs(self):
         s = self.spec
-        return (KVNeed(s.num_kv_heads, s.head_dim, s.window, value_dim=s.value_dim),)
+        if not s.own_kv:
+            return ()
+        return (KVNeed(s.num_kv_heads, s.head_dim, s.window if s.cache_window is None else s.cache_window, value_dim=s.value_dim),)
 
     def kernel_notes(self):
         s, ops = self.spec, self.env.ops
@@ -80,7 +90,7 @@ class GatedAttention(Mixer):
 
     def load(self, tensors) -> None:
         s = self.spec
-        rows = [tensors[s.q_weight], tensors[s.k_weight], tensors[s.v_weight]]
+        rows = [tensors[s.q_weight]] + ([tensors[s.k_weight], tensors[s.v_weight]] if s.own_kv else [])
         if s.gate_weight:
             rows.append(tensors[s.gate_weight])
         self.w_in = torch.cat(rows, dim=0).contiguous()  # one product for everything that reads the mixer's input
@@ -96,6 +106,8 @@ class GatedAttention(Mixer):
         if isinstance(x, NormalizedRows):
             x = x.dense(ctx)
         H, G, dk, dv = s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim
+        if cache.k is None or (not s.own_kv and cache.writes):
+            raise RuntimeError("gated attention: this layer has no keys and values of its own, and its run names no cache to read")
         if n <= 64:
             parts = ops.gemm_partials(x[:n], self.w_in, ctx.ws, "gated_attention.in_parts")
         else:
@@ -112,11 +124,12 @@ class GatedAttention(Mixer):
                 if v_first is None or v_first.shape[1] != G * dv:
                     raise RuntimeError("gated attention: a layer mixes values in, but no earlier layer of the step left values of its shape")
         q = ctx.ws.get("gated_attention.q", (n, H * dk), dt)
-        writes = cache.writes and cache.k is not None
-        ops.qkv_prep(parts, H, G, dk, dv, self.q_norm, self.k_norm, s.eps, self.cos, self.sin, ctx, ctx.block_tables[cache.group], q,
-                     cache.k if writes else None, cache.v if writes else None, role, self.mix, v_first)
+        writes = cache.writes and cache.k is not None and s.own_kv
+        wide = {"norm_wide": True} if s.norm_scope == "projection" else {}
+        ops.qkv_prep(parts, H, G if s.own_kv else 0, dk, dv, self.q_norm, self.k_norm, s.eps, self.cos, self.sin, ctx, ctx.block_tables[cache.group], q,
+                     cache.k if writes else None, cache.v if writes else None, role, self.mix, v_first, **wide)
         att = ctx.ws.get("gated_attention.out", (n, H * dv), dt)
-        g_off = H * dk + G * dk + G * dv
+        g_off = H * dk + (G * dk + G * dv if s.own_kv else 0)
         ops.gated_attention(q, cache.k, cache.v, ctx, ctx.block_tables[cache.group], att, H, G, dk, dv, s.scale, s.window, s.chunk,
                             self.sink, parts if s.gate_weight else None, g_off, **({"gate_per_head": True} if s.gate_per_head else {}))
         return add_into_stream_or_partials(ops, att, self.w_o, ctx, False, "gated_attention.delta")

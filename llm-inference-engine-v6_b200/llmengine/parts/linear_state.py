@@ -1,7 +1,9 @@
 """Recurrent mixers whose memory is a matrix per head, S [dk, dv] in float32, kept in the request's state slot and updated token
-after token by a rank-one write k v^T (ops.linear_state). Three of them, which differ in what decays the matrix, what is
+after token by a rank-one write k v^T (ops.linear_state). Four of them, which differ in what decays the matrix, what is
 written, and what the projections read:
 
+    Retention                q, k, v, g = W h;  q and k rotated at the token's position, k times a constant;  one decay a head
+                             that is a constant of the model:  S <- decay_h S + k v^T;  o = S^T q;  no weight on the heads' norm
     DecayedLinearAttention   q, k, v, g = W h;  a = sigmoid(W_a2 (W_a1 h) + b)^(1/tau) per key channel
                              S <- diag(a) S + k v^T;  o = S^T (q dk^-1/2)
     TokenShiftMix            every projection reads its own blend h + (h_prev - h) * mu of the token's input with the previous
@@ -10,7 +12,7 @@ written, and what the projections read:
     GatedDelta               q, k, v behind a short causal convolution and silu (its last inputs kept in the slot), q and k unit
                              vectors per head; g, beta per head;  S <- g S;  w = beta (v - S^T k);  S <- S + k w^T;  o = S^T q
 
-All three finish alike: every head's o divided by its root mean square, times a weight, times silu of a gate projection, then
+All of them finish alike: every head's o divided by its root mean square, times a weight, times silu of a gate projection, then
 the output projection. Decays, gates, unit norms, the state and o are float32 in both engine precisions; the projections'
 float32 sums are read as they come (K-split parts are added where they are read).
 """
@@ -22,8 +24,8 @@ import torch
 
 from .attention import add_into_stream_or_partials, project_sums
 from .base import LayerCache, Mixer, NormalizedRows, StateNeed
-from .registry import register_part
-from .spec import DecayedLinearAttentionSpec, GatedDeltaSpec, TensorNeed, TokenShiftMixSpec
+from .registry import build_part, part_class, register_part
+from .spec import DecayedLinearAttentionSpec, GatedDeltaSpec, RetentionSpec, TensorNeed, TokenShiftMixSpec
 
 
 def _state_shape(env, heads: int, dk: int, dv: int):
@@ -72,6 +74,63 @@ class DecayedLinearAttention(Mixer):
         y = ctx.ws.get("decayed_linear.y", (n, H * dv), dt)
         ops.head_norm_gate(o, self.norm_w, sums, 2 * H * dk + H * dv, s.eps, y, n, H, dv)
         return add_into_stream_or_partials(ops, y, self.w_o, ctx, False, "decayed_linear.delta")
+
+
+class Retention(Mixer):
+    """Linear attention with a fixed decay per head (RetentionSpec). The projections' float32 sums are rotated in float32
+    (ops.rotate_sums, which also applies the keys' constant), the state walks the tokens under the rule "decay_write_read" with
+    one constant row of decays, and head_norm_gate divides by the heads' root mean squares and applies silu(Wg h)."""
+
+    def __init__(self, spec: RetentionSpec, env):
+        super().__init__(spec, env)
+        if min(spec.heads, spec.dim, spec.vdim) <= 0 or len(spec.decay) != spec.heads:
+            raise ValueError("retention: sizes must be positive, and there is one decay a head")
+        self.position = build_part("position", spec.position, env)
+        tables = self.position.rotation_tables()
+        if tables is None:
+            raise ValueError("retention needs a position encoding with rotation tables")
+        self.cos, self.sin = tables
+        if self.cos is not None and 2 * self.cos.shape[1] > spec.dim:
+            raise ValueError(f"retention: {2 * self.cos.shape[1]} rotated dimensions do not fit a head of {spec.dim}")
+        self.w_in = self.w_o = self.decay = self.ones = None
+
+    @staticmethod
+    def tensor_needs(spec: RetentionSpec) -> List[TensorNeed]:
+        H, dk, dv, D = spec.heads, spec.dim, spec.vdim, spec.hidden
+        return [TensorNeed(spec.q_weight, (H * dk, D)), TensorNeed(spec.k_weight, (H * dk, D)), TensorNeed(spec.v_weight, (H * dv, D)),
+                TensorNeed(spec.g_weight, (H * dv, D)), TensorNeed(spec.o_weight, (D, H * dv))] + \
+            list(part_class("position", spec.position.kind).tensor_needs(spec.position))
+
+    def subparts(self):
+        return (self.position,)
+
+    def cache_needs(self):
+        s = self.spec
+        return (StateNeed("retention.state", _state_shape(self.env, s.heads, s.dim, s.vdim)),)
+
+    def load(self, tensors) -> None:
+        s, dev = self.spec, self.env.device
+        self.w_in = torch.cat([tensors[s.q_weight], tensors[s.k_weight], tensors[s.v_weight], tensors[s.g_weight]], dim=0).contiguous()
+        self.w_o = tensors[s.o_weight]
+        # the decays as the kernel reads them: a number a (head, key channel), one row for all tokens; float32 from the configuration's doubles
+        self.decay = torch.tensor(s.decay, dtype=torch.float64).to(torch.float32).repeat_interleave(s.dim).reshape(1, s.heads * s.dim).contiguous().to(dev)
+        self.ones = torch.ones(s.vdim, dtype=torch.float32, device=dev)
+        self.position.load(tensors)
+
+    def forward(self, x, ctx, cache: LayerCache) -> Optional[torch.Tensor]:
+        s, ops, n, dt = self.spec, self.env.ops, ctx.n_tokens, self.env.dtype
+        if isinstance(x, NormalizedRows):
+            x = x.dense(ctx)
+        H, dk, dv = s.heads, s.dim, s.vdim
+        sums = project_sums(ops, ctx, x, self.w_in, "retention.in")  # [q | k | v | g], float32, never rounded
+        qk = ctx.ws.get("retention.qk", (n, 2 * H * dk), torch.float32)
+        ops.rotate_sums(sums, 0, 2 * H, dk, self.cos, self.sin, ctx.positions, qk, n, scaled_from=H, scale=float(s.k_scale))
+        o = ctx.ws.get("retention.o", (n, H * dv), torch.float32)
+        ops.linear_state("decay_write_read", qk, 0, qk, H * dk, sums, 2 * H * dk, self.decay, 0, None, cache.states["retention.state"], ctx, o,
+                         H, H, dk, dv, decay_const=True)
+        y = ctx.ws.get("retention.y", (n, H * dv), dt)
+        ops.head_norm_gate(o, self.ones, sums, 2 * H * dk + H * dv, s.eps, y, n, H, dv)
+        return add_into_stream_or_partials(ops, y, self.w_o, ctx, False, "retention.delta")
 
 
 class TokenShiftMix(Mixer):
@@ -175,6 +234,7 @@ class GatedDelta(Mixer):
         return add_into_stream_or_partials(ops, y, self.w_o, ctx, False, "delta.delta")
 
 
+register_part("mixer", "retention", Retention)
 register_part("mixer", "decayed_linear_attention", DecayedLinearAttention)
 register_part("mixer", "token_shift_mix", TokenShiftMix)
 register_part("mixer", "gated_delta", GatedDelta)

@@ -1,5 +1,6 @@
 """RMSNorm: y = (w * x) / sqrt(mean(x^2) + eps), statistics in float32, weight used as it is
-(no 1 + w), no bias: the reference's rmsnorm_f32 (src/kernels.cpp:18-24)."""
+(no 1 + w), no bias: the reference's rmsnorm_f32 (src/kernels.cpp:18-24). Beside it the same norm with the weight stored around
+zero, and a layer norm (mean taken off, weight, no bias)."""
 from __future__ import annotations
 
 from typing import List, Optional
@@ -64,5 +65,32 @@ class UnitOffsetRMSNorm(RMSNorm):
         self.weight = (tensors[self.spec.weight] + 1.0).contiguous()
 
 
+class LayerNorm(RMSNorm):
+    """y = (x - mean) / sqrt(variance + eps) * w with the variance as the mean of the squared deviations, a weight and no bias.
+    The norm kernel with its centring switched on: the fused residual sum and the row list work as for RMSNorm. It is not of the
+    form weight * x * s(row), so it neither defers nor lets a producer prescale."""
+    can_defer = False
+
+    def forward(self, res: Residual, ctx, rows=None, n_rows=None, lazy: bool = False):
+        n = ctx.n_tokens if rows is None else (rows.numel() if n_rows is None else n_rows)
+        out = ctx.ws.get("norm.out" if rows is None else "norm.rows_out", (n, self.spec.dim), self.env.dtype)
+        self.env.ops.rmsnorm(res.h, self.weight, self.spec.eps, out, delta=res.pending, rows=rows, n_rows=n, center=True)
+        if rows is None:
+            if res.pending is not None:
+                res.sumsq = res.prescaled = res.prescaled_weight = res.operand = None  # the stream has moved on
+            res.pending = None
+        return out
+
+    def prescale_weight(self):
+        return None
+
+    def run(self, h: torch.Tensor, ctx, rows, n: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if out is None:
+            out = ctx.ws.get("norm.out" if rows is None else "norm.rows_out", (n, self.spec.dim), self.env.dtype)
+        self.env.ops.rmsnorm(h, self.weight, self.spec.eps, out, rows=rows, n_rows=n, center=True)
+        return out
+
+
 register_part("norm", "rmsnorm", RMSNorm)
+register_part("norm", "layernorm", LayerNorm)
 register_part("norm", "rmsnorm_unit_offset", UnitOffsetRMSNorm)

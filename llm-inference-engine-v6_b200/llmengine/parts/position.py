@@ -25,19 +25,22 @@ _PI_F32 = float(np.float32(3.14159265358979323846))
 def rope_inverse_frequencies(spec: PositionSpec) -> np.ndarray:
     half = spec.head_dim // 2
     theta = float(spec.theta)
+    exact = bool(getattr(spec, "float64_frequencies", False))
+    pi = math.pi if exact else _PI_F32
     inv = [1.0 / math.pow(theta, (2 * i) / spec.head_dim) for i in range(half)]
     if spec.original_max_positions > 0:
         orig = float(spec.original_max_positions)
         factor, low_f, high_f = float(spec.scaling_factor), float(spec.low_freq_factor), float(spec.high_freq_factor)
         low_wavelen, high_wavelen = orig / low_f, orig / high_f
         for i, fr in enumerate(inv):
-            wavelen = 2.0 * _PI_F32 / fr
+            wavelen = 2.0 * pi / fr
             if wavelen > low_wavelen:
                 inv[i] = fr / factor
             elif wavelen >= high_wavelen:
                 smooth = (orig / wavelen - low_f) / (high_f - low_f)
                 inv[i] = (1.0 - smooth) * fr / factor + smooth * fr
-    return np.asarray(inv, dtype=np.float64).astype(np.float32)
+    out = np.asarray(inv, dtype=np.float64)
+    return out if exact else out.astype(np.float32)
 
 
 def rope_tables(spec: PositionSpec):

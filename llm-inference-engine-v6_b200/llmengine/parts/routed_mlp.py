@@ -78,8 +78,12 @@ class GroupRoutedMLP(FeedForward):
 
         s = softmax(Wr x) or sigmoid(Wr x)  (float32);  choice = s + correction;  only the best `keep_groups` of `groups` groups stay
         (by their largest choice score, or by the sum of their two largest)
-        chosen = the `top` largest choice scores;  g_e = s_e / (sum of the chosen s + norm_eps)
-        out = sum_e g_e * Wdown_e (silu(Wgate_e x) * Wup_e x)  +  shared(x)
+        chosen = the `top` largest choice scores;  g_e = s_e / (sum of the chosen s + norm_eps) * weight_scale
+        out = sum_e g_e * Wdown_e (act(Wgate_e x, Wup_e x))  +  [sigmoid(w_sg . x) *] shared(x)
+
+    act is silu(gate) * up, or the clamped form (min(gate, L), clamp(up, -L, L), gate * sigmoid(slope * gate) * (up + 1)). With
+    `identity` > 0 the router has that many more outputs behind the experts' whose "expert" returns x itself: they take part in
+    scores and choice like the others, get no tiles in the per-expert products, and are added where the chosen rows are summed.
 
     An expert's gate and up rows are stored in turn ([E, 2 ff, hidden]: row 2 f the gate, row 2 f + 1 its up row), so that the
     per-expert product has both in one thread's hands and applies silu(gate) * up in its epilogue. Where the caller says that
@@ -88,15 +92,19 @@ class GroupRoutedMLP(FeedForward):
 
     def __init__(self, spec: GroupRoutedMLPSpec, env):
         super().__init__(spec, env)
-        if spec.activation != "silu":
-            raise ValueError(f"routed gated feed-forward: activation '{spec.activation}' is not implemented (silu is)")
-        if not (1 <= spec.top <= spec.experts):
-            raise ValueError(f"routed feed-forward: cannot choose {spec.top} of {spec.experts} experts")
-        if spec.groups < 1 or spec.experts % spec.groups or not (1 <= spec.keep_groups <= spec.groups):
-            raise ValueError(f"routed feed-forward: {spec.experts} experts do not form {spec.groups} equal groups of which {spec.keep_groups} stay")
+        if spec.activation not in ("silu", "clamped_swish") or (spec.activation == "clamped_swish" and not spec.limit > 0):
+            raise ValueError(f"routed gated feed-forward: activation '{spec.activation}' is not implemented (silu and clamped_swish with a positive limit are)")
+        self.act = (spec.activation, float(spec.limit), float(spec.slope)) if spec.activation == "clamped_swish" else spec.activation
+        if spec.identity < 0 or (spec.shared_gate and spec.shared is None):
+            raise ValueError("routed feed-forward: identity experts cannot be negative, and a gate on the shared expert needs one")
+        self.outputs = spec.experts + spec.identity  # what the router scores and chooses among
+        if not (1 <= spec.top <= self.outputs):
+            raise ValueError(f"routed feed-forward: cannot choose {spec.top} of {self.outputs} experts")
+        if spec.groups < 1 or self.outputs % spec.groups or not (1 <= spec.keep_groups <= spec.groups):
+            raise ValueError(f"routed feed-forward: {self.outputs} experts do not form {spec.groups} equal groups of which {spec.keep_groups} stay")
         if spec.score not in ("softmax", "sigmoid") or spec.group_top not in (1, 2):
             raise ValueError("routed feed-forward: score is 'softmax' or 'sigmoid', a group's score sums its 1 or 2 largest")
-        if spec.keep_groups * (spec.experts // spec.groups) < spec.top:
+        if spec.keep_groups * (self.outputs // spec.groups) < spec.top:
             raise ValueError("routed feed-forward: the groups that stay hold fewer experts than a token uses")
         if not (len(spec.gate_weights) == len(spec.up_weights) == len(spec.down_weights) == spec.experts):
             raise ValueError("routed feed-forward: one gate, one up and one down matrix per expert")
@@ -105,9 +113,12 @@ class GroupRoutedMLP(FeedForward):
 
     @staticmethod
     def tensor_needs(spec: GroupRoutedMLPSpec) -> List[TensorNeed]:
-        out = [TensorNeed(spec.router_weight, (spec.experts, spec.hidden))]
+        outputs = spec.experts + spec.identity
+        out = [TensorNeed(spec.router_weight, (outputs, spec.hidden))]
         if spec.correction:
-            out.append(TensorNeed(spec.correction, (spec.experts,), "float32", init="zeros"))
+            out.append(TensorNeed(spec.correction, (outputs,), "float32", init="zeros"))
+        if spec.shared_gate:
+            out.append(TensorNeed(spec.shared_gate, (1, spec.hidden)))
         for g, u, d in zip(spec.gate_weights, spec.up_weights, spec.down_weights):
             out += [TensorNeed(g, (spec.intermediate, spec.hidden)), TensorNeed(u, (spec.intermediate, spec.hidden)),
                     TensorNeed(d, (spec.hidden, spec.intermediate))]
@@ -128,6 +139,8 @@ class GroupRoutedMLP(FeedForward):
     def load(self, tensors) -> None:
         s = self.spec
         self.router = tensors[s.router_weight]
+        if s.shared_gate:  # the shared expert's gate is one more row behind the router's: the routing kernel forms both in float32
+            self.router = torch.cat([self.router, tensors[s.shared_gate].reshape(1, s.hidden)], dim=0).contiguous()
         self.correction = tensors[s.correction] if s.correction else None
         gu = [torch.stack([tensors[g], tensors[u]], dim=1).reshape(2 * s.intermediate, s.hidden) for g, u in zip(s.gate_weights, s.up_weights)]
         self.w_gate_up = torch.stack(gu).contiguous()                                  # [E, 2 ff, hidden], gate and up rows in turn
@@ -142,26 +155,39 @@ class GroupRoutedMLP(FeedForward):
         x = x[:n]
         idx = ctx.ws.get("routed.idx", (n, s.top), torch.int32)
         share = ctx.ws.get("routed.share", (n, s.top), torch.float32)
-        if (s.score, s.group_top, s.normalize) == ("softmax", 1, True):
-            ops.route_grouped(x, self.router, self.correction, s.top, s.groups, s.keep_groups, s.norm_eps, idx, share)
-        else:
-            ops.route_grouped(x, self.router, self.correction, s.top, s.groups, s.keep_groups, s.norm_eps, idx, share,
-                              score=s.score, group_top=s.group_top, normalize=s.normalize)
+        extra = {}
+        if (s.score, s.group_top, s.normalize) != ("softmax", 1, True):
+            extra.update(score=s.score, group_top=s.group_top, normalize=s.normalize)
+        gate = None
+        if s.weight_scale != 1.0:
+            extra["weight_scale"] = float(s.weight_scale)
+        if s.shared_gate:
+            gate = extra["gate_out"] = ctx.ws.get("routed.shared_gate", (n,), torch.float32)
+        ops.route_grouped(x, self.router, self.correction, s.top, s.groups, s.keep_groups, s.norm_eps, idx, share, **extra)
         tile = ops.routed_tile_rows(n, dt, (s.hidden, s.intermediate), n * s.top / s.experts)
-        tile_expert, tile_rows = ops.routed_group(idx, s.experts, tile, ctx.ws, "routed")
+        if s.identity:
+            tile_expert, tile_rows = ops.routed_group(idx, self.outputs, tile, ctx.ws, "routed", real_experts=s.experts)
+        else:
+            tile_expert, tile_rows = ops.routed_group(idx, s.experts, tile, ctx.ws, "routed")
         act = ctx.ws.get("routed.act", (n * s.top, s.intermediate), dt)
-        ops.routed_product(x, s.top, self.w_gate_up, tile_expert, tile_rows, act, "silu_pairs")
+        if s.activation == "silu":
+            ops.routed_product(x, s.top, self.w_gate_up, tile_expert, tile_rows, act, "silu_pairs")
+        else:
+            ops.routed_product(x, s.top, self.w_gate_up, tile_expert, tile_rows, act, "gated_pairs", act=self.act)
         y = ctx.ws.get("routed.y", (n * s.top, s.hidden), torch.float32)
         ops.routed_product(act, 1, self.w_down, tile_expert, tile_rows, y, "share", share=share.view(-1))
+        identity = (idx, share, s.experts, x) if s.identity else None
+        out = ctx.ws.get("routed.delta", (n, s.hidden), torch.float32)
         if self.shared is None:
-            out = ctx.ws.get("routed.delta", (n, s.hidden), torch.float32)
-            return ops.routed_combine(y, out, s.top)
+            return ops.routed_combine(y, out, s.top, identity=identity) if identity else ops.routed_combine(y, out, s.top)
         # the shared expert's last product, as it comes (it works for no stream here: its sums are added to the routed sum)
         keep = ctx.residual
         ctx.residual = None
         b = self.shared.forward(x, ctx)
         ctx.residual = keep
-        out = ctx.ws.get("routed.delta", (n, s.hidden), torch.float32)
+        if gate is not None or identity is not None:
+            # one kernel adds the chosen rows, the identity experts' shares of x and the shared expert's sums times its gate
+            return ops.routed_combine(y, out, s.top, identity=identity, extra=b, extra_gate=gate)
         ops.routed_combine(y, out, s.top)
         if getattr(ctx, "takes_delta_pairs", False):
             return out, b  # the caller adds the two sets of sums itself, in this order

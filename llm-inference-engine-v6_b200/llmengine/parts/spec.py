@@ -31,7 +31,7 @@ class TensorNeed:
 @dataclass(frozen=True)
 class NormSpec:
     """kind "rmsnorm": x / sqrt(mean(x^2) + eps) * weight. kind "rmsnorm_unit_offset": the same with the weight stored around
-    zero and applied as (1 + weight)."""
+    zero and applied as (1 + weight). kind "layernorm": (x - mean(x)) / sqrt(mean((x - mean(x))^2) + eps) * weight, no bias."""
     kind: str
     dim: int
     eps: float
@@ -40,7 +40,11 @@ class NormSpec:
 
 @dataclass(frozen=True)
 class PositionSpec:
-    """kind "rope": rotary, half-split layout; `scaling` as in the configuration; kind "none"."""
+    """kind "rope": rotary, half-split layout over `head_dim` numbers (a mixer that rotates only the first numbers of a head
+    names that count here); `scaling` as in the configuration: with l = 2 pi / f and original_max_positions > 0, f stays where
+    l < original / high_freq_factor, becomes f / scaling_factor where l > original / low_freq_factor, and between the two is
+    (1 - s) f / scaling_factor + s f with s = (original / l - low) / (high - low). float64_frequencies: the frequencies enter
+    the angles as float64 numbers instead of being rounded to float32 first (the reference's tables round them). kind "none"."""
     kind: str
     head_dim: int = 0
     theta: float = 10000.0
@@ -49,6 +53,7 @@ class PositionSpec:
     low_freq_factor: float = 1.0
     high_freq_factor: float = 1.0
     original_max_positions: int = 0  # 0: no rescaling of frequencies
+    float64_frequencies: bool = False
 
 
 @dataclass(frozen=True)
@@ -124,7 +129,12 @@ class GatedAttentionSpec:
     window: the last `window` keys; sink: a number per head whose exponential is one more term of the softmax's denominator;
     value_mix: "first" = this layer's values are kept for the step's tokens, "mix" = v <- (1 - m) v + m v_first with the scalar
     tensor `value_mix_weight` and the values of the step's "first" layer (the mixed values are cached);
-    gate_weight: the heads' outputs are multiplied by sigmoid(Wg h) before the output projection."""
+    gate_weight: the heads' outputs are multiplied by sigmoid(Wg h) before the output projection.
+    norm_scope "projection": q_norm [num_heads * head_dim] and k_norm [num_kv_heads * head_dim] are weights of ONE RMS norm over all
+    query heads' numbers together and one over all key heads', in place of a norm a head.
+    own_kv False: the layer has no key and value projections (no k_weight, v_weight, k_norm): its run reads the cache of the run that
+    LayerRun.cache_from names, keys as that layer normalised and rotated them. cache_window: how many of the last keys the cache
+    must keep when that is more than this layer's own window asks for, because borrowers look further back (None: `window`; 0: all)."""
     kind: str
     hidden: int
     num_heads: int
@@ -147,6 +157,9 @@ class GatedAttentionSpec:
     chunk: int = 0
     window: int = 0
     gate_per_head: bool = False            # the gate is one number a head (gate_weight [heads, hidden]) instead of one a result number
+    norm_scope: str = "head"               # "head" | "projection"
+    own_kv: bool = True
+    cache_window: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -195,6 +208,28 @@ class DecayedLinearAttentionSpec:
     a1_weight: str
     a2_weight: str
     a2_bias: str
+
+
+@dataclass(frozen=True)
+class RetentionSpec:
+    """Linear attention with one fixed decay per head and neither softmax nor denominator (kind "retention", parts/linear_state.py):
+    q = Wq h, k = Wk h (heads x dim), v = Wv h (heads x vdim); q and k rotated by `position` (any position spec with rotation tables
+    over the first numbers of a head); k times k_scale after the rotation; S <- decay_h S + k v^T; o = S^T q; every head's o is divided by
+    its root mean square (eps, no weight); out = Wo (o * silu(Wg h))."""
+    kind: str
+    hidden: int
+    heads: int
+    dim: int
+    vdim: int
+    decay: Tuple[float, ...]
+    k_scale: float
+    eps: float
+    position: object
+    q_weight: str
+    k_weight: str
+    v_weight: str
+    g_weight: str
+    o_weight: str
 
 
 @dataclass(frozen=True)
@@ -308,8 +343,12 @@ class GroupRoutedMLPSpec:
     (score "sigmoid") the sigmoid of every logit; choice scores = s + correction (optional tensor [experts]); the experts form
     `groups` equal groups of neighbours, a group's score is its largest choice score (group_top 1) or the sum of its two largest
     (group_top 2), and only experts of the best `keep_groups` groups can be chosen; the `top` largest choice scores win; their
-    weights are s (without the correction) divided by (their sum + norm_eps), or s as it is (normalize False); an expert is
-    down_e(act(gate_e x) * up_e x) without biases; `shared` (a GatedMLPSpec or None) runs for every token and is added."""
+    weights are s (without the correction) divided by (their sum + norm_eps), or s as it is (normalize False), then times
+    weight_scale; an expert is down_e(act(gate_e x) * up_e x) without biases (activation "silu", or "clamped_swish" with `limit`
+    and `slope` as in GatedMLPSpec); `shared` (a GatedMLPSpec or None) runs for every token and is added, times
+    sigmoid(shared_gate . x) (a tensor [1, hidden]) if shared_gate names one. identity: the router has `experts + identity`
+    outputs, and the last `identity` of them are experts without tensors whose result is the input x itself (scores, correction,
+    groups and the choice run over all experts + identity outputs)."""
     kind: str
     hidden: int
     intermediate: int
@@ -328,6 +367,11 @@ class GroupRoutedMLPSpec:
     score: str = "softmax"
     group_top: int = 1
     normalize: bool = True
+    weight_scale: float = 1.0
+    identity: int = 0
+    shared_gate: Optional[str] = None
+    limit: float = 0.0
+    slope: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -351,7 +395,8 @@ class TokenSideSpec:
 class BlockSpec:
     """kind "pre_norm": h += mixer(norm1(h)); h += feed_forward(norm2(h)).
     kind "parallel": h += mixer(norm1(h)) + feed_forward(norm2(h)), both of the same h (feed_forward and norm2 may be
-    None: then the mixer alone); then, if `token_input` is given, h += token_input(h, tokens).
+    None: then the mixer alone; norm2 None with a feed_forward: ONE norm, and both sub-layers read norm1(h)); then, if
+    `token_input` is given, h += token_input(h, tokens).
     kind "post_norm": the norms sit on the sub-layers' outputs and the sub-layers read h itself:
     h += scale1 * norm1(mixer(h)); h += scale2 * norm2(feed_forward(h)) (feed_forward and norm2 may be None); scale1 / scale2 name
     optional per-column layer-scale tensors [hidden].
@@ -383,21 +428,25 @@ class LayerRun:
 
 @dataclass(frozen=True)
 class EmbeddingSpec:
-    """kind "lookup": residual stream row = table row of the token id, widened to float32, times `scale`."""
+    """kind "lookup": residual stream row = table row of the token id, widened to float32, times `scale`.
+    kind "lookup_normed": the same, then `norm` (any norm spec over `dim`) applied to the row: the stream starts normalised."""
     weight: str
     vocab_size: int
     dim: int
     kind: str = "lookup"
     scale: float = 1.0
+    norm: object = None
 
 
 @dataclass(frozen=True)
 class HeadSpec:
-    """kind "linear": logits = x . W^T in float32, no bias, for the wanted rows only."""
+    """kind "linear": logits = x . W^T in float32, no bias, for the wanted rows only; with softcap c > 0 then
+    logits <- c * tanh(logits / c)."""
     weight: str  # the embedding's name when input and output embeddings are tied
     vocab_size: int
     dim: int
     kind: str = "linear"
+    softcap: float = 0.0
 
 
 @dataclass(frozen=True)

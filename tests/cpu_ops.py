@@ -18,7 +18,7 @@ class CpuOps:
         out.copy_(table[ids[:n].long()].float() * scale)
         return out
 
-    def rmsnorm(self, h, weight, eps, out, delta=None, rows=None, n_rows=None, write_back=True):
+    def rmsnorm(self, h, weight, eps, out, delta=None, rows=None, n_rows=None, write_back=True, center=False):
         if rows is not None:
             n = rows.numel() if n_rows is None else n_rows
             idx = rows[:n].long()
@@ -34,10 +34,16 @@ class CpuOps:
                 x = x + d[:n]
                 if write_back:
                     h[:n] = x
+        if center:
+            x = x - x.mean(-1, keepdim=True)
         ss = (x * x).sum(-1, keepdim=True)
         inv = 1.0 / torch.sqrt(ss / x.shape[-1] + eps)
         out[:n] = ((weight * x) * inv).to(out.dtype)
         return out
+
+    def softcap(self, x, cap):
+        x.copy_(cap * torch.tanh(x / cap))
+        return x
 
     def residual_add(self, h, delta, n_rows=None):
         n = h.shape[0] if n_rows is None else n_rows
@@ -182,8 +188,12 @@ class CpuOps:
         idx.copy_(order.to(torch.int32))
         share.copy_(torch.softmax(torch.gather(z, 1, order), dim=-1))
 
-    def route_grouped(self, x, w, correction, top, groups, keep, norm_eps, idx, share, score="softmax", group_top=1, normalize=True):
+    def route_grouped(self, x, w, correction, top, groups, keep, norm_eps, idx, share, score="softmax", group_top=1, normalize=True,
+                      weight_scale=1.0, gate_out=None):
         z = x.float() @ w.float().t()
+        if gate_out is not None:  # one more row behind the router's: a gate's logit
+            gate_out[:z.shape[0]] = torch.sigmoid(z[:, -1])
+            z = z[:, :-1]
         s = torch.sigmoid(z) if score == "sigmoid" else torch.softmax(z, dim=-1)
         choice = s + correction if correction is not None else s.clone()
         E = s.shape[1]
@@ -197,15 +207,15 @@ class CpuOps:
         order = torch.argsort(choice, dim=-1, descending=True, stable=True)[:, :top]
         picked = torch.gather(s, 1, order)
         idx.copy_(order.to(torch.int32))
-        share.copy_(picked / (picked.sum(-1, keepdim=True) + norm_eps) if normalize else picked)
+        share.copy_((picked / (picked.sum(-1, keepdim=True) + norm_eps) if normalize else picked) * weight_scale)
 
     def routed_tile_rows(self, n_tokens=0, dtype=None, inner=(), per_expert=0.0):
         return 4
 
-    def routed_group(self, idx, experts, tile, ws, tag):
+    def routed_group(self, idx, experts, tile, ws, tag, real_experts=None):
         flat = idx.reshape(-1).tolist()
         tiles_e, tiles_r = [], []
-        for e in range(experts):
+        for e in range(experts if real_experts is None else real_experts):
             rows = [p for p, ex in enumerate(flat) if ex == e]
             for i in range(0, len(rows), tile):
                 chunk = rows[i:i + tile]
@@ -217,7 +227,7 @@ class CpuOps:
             tiles_r.append([-1] * tile)
         return torch.tensor(tiles_e, dtype=torch.int32), torch.tensor(tiles_r, dtype=torch.int32)
 
-    def routed_product(self, a, a_div, w, tile_expert, tile_rows, out, epilogue, share=None):
+    def routed_product(self, a, a_div, w, tile_expert, tile_rows, out, epilogue, share=None, act="silu"):
         for e, rows in zip(tile_expert.tolist(), tile_rows.tolist()):
             if e < 0:
                 continue
@@ -229,13 +239,25 @@ class CpuOps:
                     v = 0.5 * v * (1.0 + torch.erf(v / 2.0 ** 0.5))
                 elif epilogue == "share":
                     v = v * share[p]
+                elif epilogue == "gated_pairs":
+                    v = self._glu(v[0::2], v[1::2], act)
                 else:  # "silu_pairs": rows 2 f and 2 f + 1 are a gate and its up row
                     v = torch.nn.functional.silu(v[0::2]) * v[1::2]
                 out[p] = v.to(out.dtype)
         return out
 
-    def routed_combine(self, y, out, top):
-        out.copy_(y.view(out.shape[0], top, -1).sum(1))
+    def routed_combine(self, y, out, top, identity=None, extra=None, extra_gate=None):
+        n = out.shape[0]
+        rows = y.view(n, top, -1).clone()
+        if identity is not None:
+            idx, share, real, x = identity
+            own = (idx >= real)[:, :, None]
+            rows = torch.where(own, share[:, :, None] * x[:n].float()[:, None, :], rows)
+        total = rows.sum(1)
+        if extra is not None:
+            b = (extra if extra.dim() == 2 else extra.sum(0))[:n]
+            total = total + (b * extra_gate[:n, None] if extra_gate is not None else b)
+        out.copy_(total)
         return out
 
     def rope_kv_write(self, qkv, positions, token_seq, block_table, cos, sin, kcache, vcache, n_tokens, nq, nkv, hd, parts=None):
@@ -276,7 +298,7 @@ class CpuOps:
         return h
 
     def qkv_prep(self, parts, heads, kv_heads, dk, dv, q_norm, k_norm, eps, cos, sin, batch, block_table, q_out, kcache, vcache,
-                 mix_role=0, mix_weight=None, v_first=None):
+                 mix_role=0, mix_weight=None, v_first=None, norm_wide=False):
         src = parts.sum(0)
         half = 0 if cos is None else cos.shape[1]
         for t in range(batch.n_tokens):
@@ -286,7 +308,9 @@ class CpuOps:
             k = row[heads * dk:(heads + kv_heads) * dk].view(kv_heads, dk).clone()
             v = row[(heads + kv_heads) * dk:(heads + kv_heads) * dk + kv_heads * dv].clone()
             for x, w in ((q, q_norm), (k, k_norm)):
-                if w is not None:
+                if w is not None and x.numel() and norm_wide:  # one norm over the whole projection, a weight a number
+                    x.copy_(x / torch.sqrt((x * x).mean() + eps) * w.view(x.shape))
+                elif w is not None and x.numel():
                     x.copy_(x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * w)
                 if half:
                     a, b = x[:, :half].clone(), x[:, half:2 * half].clone()
@@ -401,7 +425,7 @@ class CpuOps:
         return (t if t.dim() == 2 else t.sum(0))[:, off:off + width]
 
     def linear_state(self, rule, q, q_off, k, k_off, v, v_off, decay, decay_off, bonus, state, batch, out, heads, kv_heads, dk, dv,
-                     q_scale=1.0, unit_eps=-1.0):
+                     q_scale=1.0, unit_eps=-1.0, decay_const=False):
         Q = self._cols(q, q_off, kv_heads * dk).reshape(-1, kv_heads, dk) * q_scale
         K = self._cols(k, k_off, kv_heads * dk).reshape(-1, kv_heads, dk)
         V = self._cols(v, v_off, heads * dv).reshape(-1, heads, dv)
@@ -422,7 +446,7 @@ class CpuOps:
                     S = S + kt[:, :, None] * w[:, None, :]
                     o = torch.einsum("hkv,hk->hv", S, qt)
                 else:
-                    a = decay[t, decay_off:decay_off + heads * dk].view(heads, dk)
+                    a = decay[0 if decay_const else t, decay_off:decay_off + heads * dk].view(heads, dk)
                     if rule == "decay_write_read":
                         S = a[:, :, None] * S + kv
                         o = torch.einsum("hkv,hk->hv", S, qt)
@@ -431,6 +455,19 @@ class CpuOps:
                         S = a[:, :, None] * S + kv
                 out[t] = o.reshape(-1)
             state[slot] = S
+        return out
+
+    def rotate_sums(self, x, x_off, heads, dk, cos, sin, positions, out, n_tokens, scaled_from=None, scale=1.0):
+        rows = self._cols(x, x_off, heads * dk)[:n_tokens].reshape(n_tokens, heads, dk).clone()
+        if cos is not None:
+            half = cos.shape[1]
+            c, s = cos[positions[:n_tokens].long()][:, None, :], sin[positions[:n_tokens].long()][:, None, :]
+            u, v = rows[:, :, :half].clone(), rows[:, :, half:2 * half].clone()
+            rows[:, :, :half] = u * c - v * s
+            rows[:, :, half:2 * half] = v * c + u * s
+        if scaled_from is not None:
+            rows[:, scaled_from:] *= scale
+        out[:n_tokens] = rows.reshape(n_tokens, heads * dk)
         return out
 
     def token_shift(self, x, mu, shift_state, batch, out):
