@@ -262,3 +262,23 @@ class Plain:
         if cap:
             logits = cap * torch.tanh(logits / cap)
         return logits
+
+
+def forward(cfg, w, ids, after_layers=None):
+    """Logits [T, vocab] of a whole sequence; after_layers (a list) receives the stream behind every layer."""
+    m = Plain(cfg, w)
+    out = m.run(list(ids))
+    if after_layers is not None:
+        after_layers.extend(m.streams)
+    return out
+
+
+def greedy(cfg, w, prompt, n_new):
+    """prompt + n_new tokens, each the first index of the largest logit; the sequence's keys and states are carried."""
+    m = Plain(cfg, w)
+    out = list(prompt)
+    logits = m.run(out)
+    for _ in range(n_new):
+        out.append(int(torch.argmax(logits[-1])))
+        logits = m.run(out[-1:])
+    return out
