@@ -506,7 +506,33 @@ SELINEX_SIZES = {
     "w1024": (selinex_sizes(1024, 16, 4, 64, 1024, 8, 128, 2816, 8, 2, 4, 2, 1408, 4, 32768), ZULOPEL_SIZES["w1024"][0]),
     "w2048": (selinex_sizes(2048, 32, 8, 64, 1024, 16, 128, 8192, 16, 4, 4, 2, 2048, 4, 32768), ZULOPEL_SIZES["w2048"][0]),
 }
-DESIGNS = {"vapelix": DESIGN_SIZES, "zulopel": ZULOPEL_SIZES, "selinex": SELINEX_SIZES}
+
+
+def sogutar_sizes(width, heads, kv_heads, dim, window, state_heads, state_dim, ff, experts, identity, top, expert_ff, shared_ff, layers, vocab):
+    def att(kv_from=None):
+        m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "mask": {"size": window},
+             "rot": {"dims": dim // 2, "base": 500000.0, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 4096}}}
+        if kv_from is not None:
+            m["kv_from"] = kv_from
+        return m
+    ret = {"heads": state_heads, "dim": state_dim, "vdim": state_dim, "decay": [1.0 - 2.0 ** (-5.0 - 5.0 * h / max(state_heads - 1, 1)) for h in range(state_heads)],
+           "rot": {"dims": state_dim, "base": 10000.0}}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff, "limit": 7.0}, "router": {"experts": experts, "identity": identity, "top": top, "scale": 2.0},
+           "shared": {"ff": shared_ff, "limit": 7.0}}
+    kinds = [("attention", att(), dense), ("retention", ret, moe), ("attention", att(0), moe), ("retention", ret, moe)]
+    return {"architecture": "Sogutar", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_softcap": 30.0, "max_positions": 8192,
+            "layers": [{"type": t, "mixer": m, "mlp": f} for t, m, f in (kinds[i % 4] for i in range(layers))]}
+
+
+# Sogutar: windowed attention (the third layer on the first layer's keys and values) in turn with retention layers, a dense feed-forward and
+# clamped routed experts with identity experts and a gated shared expert; beside it the Selinex configuration of the same name (windowed
+# attention, linear-state mixers, routed and clamped feed-forwards: the closest existing model)
+SOGUTAR_SIZES = {
+    "w1024": (sogutar_sizes(1024, 16, 4, 64, 1024, 8, 128, 2816, 8, 2, 2, 1408, 1408, 4, 32768), SELINEX_SIZES["w1024"][0]),
+    "w2048": (sogutar_sizes(2048, 32, 8, 64, 1024, 16, 128, 8192, 16, 2, 4, 2048, 2048, 4, 32768), SELINEX_SIZES["w2048"][0]),
+}
+DESIGNS = {"vapelix": DESIGN_SIZES, "zulopel": ZULOPEL_SIZES, "selinex": SELINEX_SIZES, "sogutar": SOGUTAR_SIZES}
 
 
 def run_design(args):

@@ -116,6 +116,72 @@ __global__ void __launch_bounds__(PREP_WARPS * 32)
   }
 }
 
+// The same work for norm_wide when a token's whole [q | k] row fits shared memory: ONE block a token forms the row's sums once
+// (the parts added in their order), leaves them in shared memory with both sums of squares, and then a warp a head normalises,
+// rotates and writes. A step of few tokens runs it with many warps (a head a warp at once); the other kernel would read every
+// part twice and repeat the statistic in each of a token's blocks.
+template <typename T>
+__global__ void __launch_bounds__(512)
+    qkv_prep_wide_kernel(const float* __restrict__ parts, int n_parts, size_t pstride, int width, int H, int G, int dk, int dv, int rot_dims,
+                         const float* __restrict__ wq, const float* __restrict__ wk, float eps, const float* __restrict__ cos_t,
+                         const float* __restrict__ sin_t, const int* __restrict__ positions, const int* __restrict__ token_seq,
+                         const int* __restrict__ block_table, int max_blocks, T* __restrict__ q_out, long long ld_q, T* __restrict__ kcache,
+                         T* __restrict__ vcache, int page_size) {
+  extern __shared__ float row_s[];  // (H + G) * dk
+  __shared__ float red[33];
+  dep_launch();
+  dep_wait();
+  const int tok = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = blockDim.x >> 5;
+  const int pos = positions[tok];
+  const size_t row = (size_t)tok * width;
+  const int half = rot_dims / 2, nq = H * dk, nk = G * dk;
+  float ssq = 0.f, ssk = 0.f;
+  for (int i = threadIdx.x; i < nq + nk; i += blockDim.x) {
+    const float v = parts_sum(parts, n_parts, pstride, row + i);
+    row_s[i] = v;
+    if (i < nq) ssq += v * v;
+    else ssk += v * v;
+  }
+  const float inv_q = wq ? 1.0f / sqrtf(block_sum(ssq, red) / (float)nq + eps) : 1.0f;
+  const float inv_k = (wk && G > 0) ? 1.0f / sqrtf(block_sum(ssk, red) / (float)nk + eps) : 1.0f;
+  __syncthreads();
+  const float* cs = cos_t ? cos_t + (size_t)pos * half : nullptr;
+  const float* sn = sin_t ? sin_t + (size_t)pos * half : nullptr;
+  const int page = block_table[(size_t)token_seq[tok] * max_blocks + pos / page_size];
+  const int in_page = pos % page_size;
+  for (int head = warp; head < H + G; head += n_warps) {
+    const bool is_q = head < H;
+    const float* w = is_q ? wq : wk;
+    const float inv = is_q ? inv_q : inv_k;
+    const float* buf = row_s + (size_t)head * dk;  // key heads lie right behind the query heads, in the row as in the product
+    const float* wh = w ? w + (size_t)(is_q ? head : head - H) * dk : nullptr;
+    T* dst;
+    if (is_q) dst = q_out + (size_t)tok * ld_q + (size_t)head * dk;
+    else dst = kcache ? kcache + (((size_t)page * G + (head - H)) * page_size + in_page) * dk : nullptr;
+    if (!dst) continue;
+    for (int d = lane; d < dk; d += 32) {
+      const float x = wh ? buf[d] * inv * wh[d] : buf[d];
+      float v = x;
+      if (d < half) {
+        const float y = wh ? buf[d + half] * inv * wh[d + half] : buf[d + half];
+        v = x * cs[d] - y * sn[d];
+      } else if (d < rot_dims) {
+        const float y = wh ? buf[d - half] * inv * wh[d - half] : buf[d - half];
+        v = x * cs[d - half] + y * sn[d - half];
+      }
+      dst[d] = from_f32<T>(v);
+    }
+  }
+  if (vcache) {
+    const size_t vcol0 = (size_t)(H + G) * dk;
+    for (int i = threadIdx.x; i < G * dv; i += blockDim.x) {
+      const float v = parts_sum(parts, n_parts, pstride, row + vcol0 + i);
+      const int g = i / dv, d = i - g * dv;
+      vcache[(((size_t)page * G + g) * page_size + in_page) * dv + d] = from_f32<T>(v);
+    }
+  }
+}
+
 constexpr int WARPS = 4;
 constexpr int MAX_HD = 256;
 
@@ -225,6 +291,21 @@ extern "C" int llm_qkv_prep(const float* parts, int n_parts, long long pstride, 
   LLM_REQUIRE(mix_role == 0 || (v_first && (mix_role == 1 || (mix_role == 2 && lambda))), "qkv_prep: value mixing needs its buffer and weight");
   const size_t smem = (size_t)PREP_WARPS * dk * sizeof(float);
   LLM_REQUIRE(smem <= 48 * 1024, "qkv_prep: a head of %d numbers exceeds one block's shared memory", dk);
+  const size_t wide_smem = (size_t)(H + G) * dk * sizeof(float);
+  if (norm_wide && mix_role == 0 && wide_smem <= 40 * 1024) {
+    // a block a token; with few tokens as many warps as there are heads (up to 16), with many tokens four
+    int warps = n_tokens >= 512 ? 4 : min(16, max(4, H + G));
+#define LLM_PREP_WIDE(T)                                                                                                             \
+  launch_kernel(qkv_prep_wide_kernel<T>, n_tokens, warps * 32, wide_smem, stream, parts, n_parts, (size_t)pstride, width, H, G, dk, dv, \
+                rot_dims, wq, wk, eps, cos_t, sin_t, positions, token_seq, block_table, max_blocks, (T*)q_out, ld_q, (T*)kcache,       \
+                (T*)vcache, page_size)
+    if (dtype == LLM_F32) LLM_PREP_WIDE(float);
+    else if (dtype == LLM_BF16) LLM_PREP_WIDE(bf16);
+    else LLM_REQUIRE(false, "qkv_prep: unknown dtype %d", dtype);
+#undef LLM_PREP_WIDE
+    LLM_CHECK_LAUNCH("qkv_prep");
+    return LLM_OK;
+  }
   // few tokens: the heads of a token are spread over several blocks, so that the sums of many parts are read side by side
   dim3 grid(n_tokens, n_tokens >= 512 ? 1 : min(ceil_div(H + G, PREP_WARPS), 8));
 #define LLM_PREP(T)                                                                                                                  \

@@ -480,21 +480,22 @@ __global__ void rotate_sums_kernel(Sums x, int heads, int dk, int rot_dims, cons
                                    const int* __restrict__ positions, float* __restrict__ out, int n_tokens, int scaled_from, float scale) {
   dep_launch();
   dep_wait();
-  const int per = heads * dk;
+  // a thread a pair of the rotated part, or a single number behind it: dk - half items a head, every number read and written once
+  const int half = rot_dims / 2, items = dk - half, per = heads * items;
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (size_t)n_tokens * per) return;
-  const int tok = (int)(i / per), c = (int)(i - (size_t)tok * per), head = c / dk, d = c - head * dk, half = rot_dims / 2;
-  const size_t at = (size_t)tok * x.width + x.off + c;
-  float v = parts_sum(x.p, x.n, x.stride, at);
-  if (d < rot_dims) {
-    const int pr = d < half ? d : d - half;
-    const float cs = cos_t[(size_t)positions[tok] * half + pr], sn = sin_t[(size_t)positions[tok] * half + pr];
-    const float other = parts_sum(x.p, x.n, x.stride, d < half ? at + half : at - half);
-    v = d < half ? v * cs - other * sn : v * cs + other * sn;
+  const int tok = (int)(i / per), c = (int)(i - (size_t)tok * per), head = c / items, j = c - head * items;
+  const float mul = head >= scaled_from ? scale : 1.0f;
+  const size_t src = (size_t)tok * x.width + x.off + (size_t)head * dk, dst = ((size_t)tok * heads + head) * dk;
+  if (j < half) {
+    const float u = parts_sum(x.p, x.n, x.stride, src + j), v = parts_sum(x.p, x.n, x.stride, src + j + half);
+    const float cs = cos_t[(size_t)positions[tok] * half + j], sn = sin_t[(size_t)positions[tok] * half + j];
+    out[dst + j] = (u * cs - v * sn) * mul;
+    out[dst + j + half] = (v * cs + u * sn) * mul;
+  } else {
+    out[dst + j + half] = parts_sum(x.p, x.n, x.stride, src + j + half) * mul;
   }
-  out[i] = head >= scaled_from ? v * scale : v;
 }
-
 
 int lanes_for(int dk) {
   int r = 1;
@@ -622,7 +623,7 @@ extern "C" int llm_rotate_sums(const float* x, int xn, long long xs, int xw, int
   if (n_tokens == 0) return LLM_OK;
   LLM_REQUIRE(n_tokens > 0 && heads > 0 && dk > 0 && x && out && xn >= 1 && xo >= 0 && (long long)xo + (long long)heads * dk <= xw, "rotate_sums: bad arguments");
   LLM_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= dk && (rot_dims == 0 || (cos_t && sin_t && positions)), "rotate_sums: %d rotated numbers in a head of %d", rot_dims, dk);
-  launch_kernel(rotate_sums_kernel, ceil_div((long long)n_tokens * heads * dk, 256), 256, 0, stream, Sums{x, xn, (size_t)xs, xw, xo}, heads, dk,
+  launch_kernel(rotate_sums_kernel, ceil_div((long long)n_tokens * heads * (dk - rot_dims / 2), 256), 256, 0, stream, Sums{x, xn, (size_t)xs, xw, xo}, heads, dk,
                 rot_dims, cos_t, sin_t, positions, out, n_tokens, scaled_from, scale);
   LLM_CHECK_LAUNCH("rotate_sums");
   return LLM_OK;
