@@ -204,11 +204,11 @@ def _attention_layer(heads, kv_heads, dim, vdim, window, rot, scaling=None):
 ATTENTION_CASES = [(SOGUTAR_A, 1), (SOGUTAR_B, 0), (SOGUTAR_B, 2), (SOGUTAR_C, 0), (SOGUTAR_C, 3),
                    (_attention_layer(6, 2, 64, 32, 16, (24, 1000.0), (4.0, 1.0, 4.0, 32)), 0), (_attention_layer(8, 1, 128, 128, None, None), 0),
                    (_attention_layer(2, 2, 32, 128, 7, (32, 5e5)), 0), (_attention_layer(12, 3, 128, 64, 21, (64, 100.0), (2.0, 0.5, 2.0, 16)), 0),
-                   (_attention_layer(4, 1, 96, 96, 30, (48, 1e4)), 0)]
+                   (_attention_layer(6, 2, 96, 48, 30, (24, 1e4)), 0)]
 
 
 @pytest.mark.parametrize("dt", DTYPES)
-@pytest.mark.parametrize("cfg,i", ATTENTION_CASES, ids=["a1", "b0", "b2", "c0", "c3", "64x32", "128x128", "32x128", "128x64", "96x96"])
+@pytest.mark.parametrize("cfg,i", ATTENTION_CASES, ids=["a1", "b0", "b2", "c0", "c3", "64x32", "128x128", "32x128", "128x64", "96x48"])
 @pytest.mark.parametrize("sharp", [False, True])
 def test_attention_alone(dt, cfg, i, sharp):
     """A layer with keys of its own over a prompt portion, then over single tokens and further portions that read the first one's
@@ -518,6 +518,37 @@ def test_long_decoding_and_generation(model):
     else:  # bfloat16: close to the plain logits' best; a router's choice that rounding flips may move single positions further
         off = [p for p in range(10, 100) if logits[p, out[p + 1]] < logits[p].max() - 0.1 * max(1.0, np.abs(logits[p]).max())]
         assert len(off) <= 9, f"{len(off)} of 90 generated tokens are far from the plain logits' best, first at {off[0]}"
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("dim,vdim,window", [(64, 64, 136), (64, 64, None), (128, 128, 700), (32, 64, 200), (48, 48, 136)])
+def test_single_tokens_behind_long_contexts(dt, dim, vdim, window, tmp_path):
+    """Three requests of unequal length (up to 1,500 tokens) whose last tokens come one a step, side by side: single tokens whose
+    key range is cut into pieces that run side by side and are merged, with a window that ends inside a piece, begins behind
+    whole pieces, or is absent; an attention layer on borrowed keys and a retention layer behind it."""
+    layers = [{"type": "attention", "mixer": att(4, 2, dim, vdim, dim ** -0.5, window, (dim // 2, 1e4), (4.0, 1.0, 4.0, 256)), "mlp": dense(64)},
+              {"type": "retention", "mixer": ret(2, 32, 48, (0.99, 0.999), (16, 100.0)), "mlp": None},
+              {"type": "attention", "mixer": att(4, 2, dim, vdim, 0.1, 90 if window else 300, (dim // 2, 1e4), (4.0, 1.0, 4.0, 256), kv_from=0), "mlp": None}]
+    cfg = {"architecture": "Sogutar", "vocab": 120, "width": 64, "norm": {"eps": 1e-5}, "logit_softcap": 20.0, "max_positions": 2048, "layers": layers}
+    d = write_model(str(tmp_path / "m"), cfg, dt, sharp=True)
+    pc, pw = P.read_model(d)
+    reqs = {"a": random_ids(1500, 120, 1), "b": random_ids(700, 120, 2), "c": random_ids(200, 120, 3)}
+    tail = 24
+    eng = llmengine.Engine(d, NAMES[dt], block_size=16)
+    eng.configure_cache(num_blocks=(1536 + 704 + 256) // 16, block_size=16, num_slots=4)
+    ids = {"a": 1, "b": 2, "c": 3}
+    for k, v in reqs.items():
+        eng.run_step([(ids[k], v[:-tail], [])], end=[])
+    rows = {k: [] for k in reqs}
+    for t in range(tail):
+        batch = [(ids[k], [v[len(v) - tail + t]], [0]) for k, v in reqs.items()]
+        lg = eng.run_step(batch, end=list(ids.values()) if t == tail - 1 else []).float().cpu().numpy()
+        for i, k in enumerate(reqs):
+            rows[k].append(lg[i].copy())
+    for k, v in reqs.items():
+        want = P.forward(pc, pw, v).numpy()[-tail:]
+        rounded = rounded_forward(pc, pw, v)[-tail:] if dt == torch.bfloat16 else None
+        rows_close(np.stack(rows[k]), want, dt, f"request {k}", rounded)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

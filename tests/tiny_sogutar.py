@@ -61,7 +61,7 @@ SOGUTAR_A = {"architecture": "Sogutar", "vocab": 301, "width": 72, "norm": {"eps
 #    identity experts; no cap on the logits; a borrower with a NARROWER window; pages of 16
 SOGUTAR_B = {"architecture": "Sogutar", "vocab": 512, "width": 128, "norm": {"eps": 1e-6}, "max_positions": 1024,
              "layers": [{"type": "attention", "mixer": att(4, 2, 64, 64, 0.125, 48, (32, 250000.0), (8.0, 1.0, 4.0, 64)), "mlp": dense(256)},
-                        {"type": "retention", "mixer": ret(4, 32, 64, (0.96875, 0.99, 0.998, 0.9995), (32, 1e6)), "mlp": moe(64, 1.0, 6, 2, 3, 2.5, (128, 2.0))},
+                        {"type": "retention", "mixer": ret(4, 32, 96, (0.96875, 0.99, 0.998, 0.9995), (32, 5e5)), "mlp": moe(48, 1.25, 6, 2, 3, 2.5, (128, 2.0))},
                         {"type": "attention", "mixer": att(4, 4, 32, 128, 0.18, 40, (16, 10000.0)), "mlp": moe(64, 2.0, 16, 0, 4, 1.0, (64, 1.0))},
                         {"type": "attention", "mixer": att(4, 2, 64, 64, 0.1, 17, (32, 250000.0), (8.0, 1.0, 4.0, 64), kv_from=0), "mlp": dense(128)},
                         {"type": "retention", "mixer": ret(2, 64, 128, (0.9, 0.9999), (16, 100.0)), "mlp": dense(384)}]}
